@@ -1,0 +1,64 @@
+"""Builds libaccy_b200.so (C++17 host library behind the C ABI) in-tree with g++.
+
+The library links neither libcuda nor libnvrtc (both are dlopen'ed at run time), so it builds and
+loads on machines without a GPU.  Kernels are CUDA templates the library instantiates per program
+and compiles for sm_100a through NVRTC; `check_kernels_with_nvcc` cross-compiles the same sources
+with nvcc to prove they build and to record registers/spills/shared memory (-Xptxas -v).
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libaccy_b200.so")
+SOURCES = ["program.cpp", "wire.cpp", "planner.cpp", "emit_row.cpp", "emit_gemm.cpp", "emit_tc.cpp",
+           "driver.cpp", "session.cpp"]
+
+
+def needs_build():
+    if not os.path.exists(LIB):
+        return True
+    built = os.path.getmtime(LIB)
+    for name in os.listdir(CSRC):
+        if os.path.getmtime(os.path.join(CSRC, name)) > built:
+            return True
+    return os.path.getmtime(os.path.join(HERE, "..", "include", "accy_b200.h")) > built
+
+
+def build(force=False, verbose=False):
+    if not force and not needs_build():
+        return LIB
+    cmd = ["g++", "-std=c++17", "-O2", "-g", "-fPIC", "-shared", "-Wall", "-Wextra", "-Wno-unused-parameter",
+           "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES] + ["-ldl", "-lpthread"]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return LIB
+
+
+def check_kernels_with_nvcc(sources, out_dir, verbose=False):
+    """Cross-compiles generated kernel sources for sm_100a with nvcc; returns ptxas -v text per kernel.
+
+    `sources` is a list of (name, cuda_source, options) as returned by CompiledProgram.kernels().
+    """
+    os.makedirs(out_dir, exist_ok=True)
+    reports = {}
+    for name, source, options in sources:
+        cu = os.path.join(out_dir, name + ".cu")
+        with open(cu, "w") as f:
+            f.write(source)
+        cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+               "-Xptxas", "-v", "-cubin", "-o", os.path.join(out_dir, name + ".cubin"), cu]
+        cmd += [o for o in options.split() if o.startswith("--fmad")]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed for %s:\n%s" % (name, proc.stderr))
+        reports[name] = proc.stderr
+        if verbose:
+            print(proc.stderr)
+    return reports
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose=True))

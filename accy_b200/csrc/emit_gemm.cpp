@@ -1,0 +1,137 @@
+// CUDA source emission for contractions: the k-serial SIMT dot kernel (any shape, any strides,
+// f32/f16/bf16) and the shared epilogue emitter.  The tcgen05 kernels live in emit_tc.cpp.
+//
+// The SIMT kernel restates the reference's generic dot lowering
+// (src/preparation/kernelization/lowering/dot.zig:2049-2115): one thread per output element,
+// k folded serially as acc = acc + a*b with separate multiply and add roundings (compiled with
+// --fmad=false), 16-bit inputs widened to f32 and narrowed once at the end (:2004-2015).  It is
+// the exact-order path used for f32 programs and for shapes the tensor-core tiles do not cover.
+#include <sstream>
+
+#include "plan.hpp"
+
+namespace accy {
+
+void emitGemmTcgen05(const GemmOp& g, const std::string& name, Plan& plan, const ScheduleOverrides& o);
+
+namespace {
+
+std::string loadConv(DType d, const std::string& raw) {
+  if (d == DType::bf16) return "bf16_to_f32(" + raw + ")";
+  if (d == DType::f16) return "f16_to_f32(" + raw + ")";
+  return raw;
+}
+
+std::string storeConv(DType d, const std::string& v) {
+  if (d == DType::bf16) return "f32_to_bf16(" + v + ")";
+  if (d == DType::f16) return "f32_to_f16(" + v + ")";
+  if (d == DType::i1) return "(unsigned char)(" + v + " ? 1 : 0)";
+  return v;
+}
+
+}  // namespace
+
+const char* kConvertPrelude = R"CUDA(
+__device__ __forceinline__ float bf16_to_f32(unsigned short h) { return __uint_as_float(((unsigned int)h) << 16); }
+__device__ __forceinline__ unsigned short f32_to_bf16(float f) { unsigned short r; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f)); return r; }
+__device__ __forceinline__ float f16_to_f32(unsigned short h) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h)); return f; }
+__device__ __forceinline__ unsigned short f32_to_f16(float f) { unsigned short r; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(r) : "f"(f)); return r; }
+)CUDA";
+
+// Emits statements computing the epilogue for one accumulator element.  `acc` names the f32
+// accumulator, (bi, mi, ni) name the element's coordinates, leaf k is pointer E<k>.  Returns the
+// name of the value to store; with an empty epilogue that is `acc` itself.
+std::string emitEpilogueBody(const Epilogue& ep, std::ostringstream& o, const std::string& indent,
+                             const std::string& acc, const std::string& bi, const std::string& mi,
+                             const std::string& ni, const std::string& suffix) {
+  if (ep.nodes.empty() || ep.result < 0) return acc;
+  auto nm = [&](int i) { return i == ep.acc ? acc : "e" + std::to_string(i) + suffix; };
+  for (size_t i = 0; i < ep.nodes.size(); ++i) {
+    const ENode& n = ep.nodes[i];
+    if (static_cast<int>(i) == ep.acc) continue;
+    o << indent << "const " << ctypeOf(n.dtype) << " " << nm(static_cast<int>(i)) << " = ";
+    switch (n.op) {
+      case ENode::Leaf: {
+        const LeafRef& l = ep.leaves[n.leaf];
+        std::ostringstream idx;
+        idx << "(long long)" << bi << " * " << l.strides[0] << "ll + (long long)" << mi << " * " << l.strides[1]
+            << "ll + (long long)" << ni << " * " << l.strides[2] << "ll";
+        o << loadConv(l.dtype, "E" + std::to_string(n.leaf) + "[" + idx.str() + "]");
+        break;
+      }
+      case ENode::Const: o << constLiteral(n); break;
+      case ENode::Iota: throw PlanError("iota inside a GEMM epilogue is not supported");
+      case ENode::Red: throw PlanError("reduction inside a GEMM epilogue is not supported");
+      default: {
+        std::string a = n.args[0] >= 0 ? nm(n.args[0]) : "", b = n.args[1] >= 0 ? nm(n.args[1]) : "",
+                    c = n.args[2] >= 0 ? nm(n.args[2]) : "";
+        o << elementwiseExpr(n, a, b, c, ep.nodes[n.args[n.op == ENode::Sel ? 1 : 0]].dtype);
+      }
+    }
+    o << ";\n";
+  }
+  return nm(ep.result);
+}
+
+std::string epilogueParams(const Epilogue& ep) {
+  std::ostringstream p;
+  for (size_t k = 0; k < ep.leaves.size(); ++k)
+    p << ", const " << storageTypeOf(ep.leaves[k].dtype) << "* __restrict__ E" << k;
+  return p.str();
+}
+
+static void emitGemmSimt(const GemmOp& g, const std::string& name, Plan& plan) {
+  std::ostringstream o;
+  const char* in_t = storageTypeOf(g.in_dtype);
+  const char* out_t = storageTypeOf(g.out_dtype);
+  o << kConvertPrelude;
+  o << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const " << in_t
+    << "* __restrict__ A, const " << in_t << "* __restrict__ B, " << out_t << "* __restrict__ C"
+    << epilogueParams(g.epilogue) << ") {\n";
+  o << "  const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;\n";
+  o << "  if (idx >= " << g.batch * g.m * g.n << "ll) return;\n";
+  o << "  const long long ni = idx % " << g.n << "ll;\n  const long long mi = (idx / " << g.n << "ll) % " << g.m
+    << "ll;\n  const long long bi = idx / " << g.m * g.n << "ll;\n";
+  o << "  const " << in_t << "* a = A + bi * " << g.a_stride_b << "ll + mi * " << g.a_stride_m << "ll;\n";
+  o << "  const " << in_t << "* b = B + bi * " << g.b_stride_b << "ll + ni * " << g.b_stride_n << "ll;\n";
+  o << "  float acc = 0.0f;\n";
+  o << "  for (long long k = 0; k < " << g.k << "ll; ++k) {\n";
+  o << "    const float av = " << loadConv(g.in_dtype, "a[k * " + std::to_string(g.a_stride_k) + "ll]") << ";\n";
+  o << "    const float bv = " << loadConv(g.in_dtype, "b[k * " + std::to_string(g.b_stride_k) + "ll]") << ";\n";
+  o << "    const float prod = av * bv;\n    acc = acc + prod;\n  }\n";
+  std::string result = emitEpilogueBody(g.epilogue, o, "  ", "acc", "bi", "mi", "ni", "");
+  o << "  C[idx] = " << storeConv(g.out_dtype, result) << ";\n}\n";
+  KernelSource ks;
+  ks.name = name;
+  ks.family = "gemm_simt";
+  ks.source = o.str();
+  ks.options.push_back("--fmad=false");
+  plan.kernels.push_back(ks);
+  Launch l;
+  l.kernel = static_cast<int>(plan.kernels.size()) - 1;
+  const long long total = g.batch * g.m * g.n;
+  if ((total + 255) / 256 > 0x7fffffffll) throw PlanError("dot_general output too large for the SIMT kernel");
+  l.grid[0] = static_cast<uint32_t>((total + 255) / 256);
+  l.block[0] = 256;
+  l.label = name;
+  KernelArg a;
+  a.slot = g.a_slot;
+  l.args.push_back(a);
+  a.slot = g.b_slot;
+  l.args.push_back(a);
+  a.slot = g.c_slot;
+  l.args.push_back(a);
+  for (const LeafRef& leaf : g.epilogue.leaves) {
+    a.slot = leaf.slot;
+    l.args.push_back(a);
+  }
+  plan.launches.push_back(l);
+}
+
+void emitGemm(const GemmOp& g, const std::string& name, Plan& plan, const ScheduleOverrides& o) {
+  if (g.in_dtype == DType::f64) throw PlanError("f64 dot_general is not supported");
+  if (g.tensor_core) emitGemmTcgen05(g, name, plan, o);
+  else emitGemmSimt(g, name, plan);
+}
+
+}  // namespace accy

@@ -86,18 +86,18 @@ static void emitGemmSimt(const GemmOp& g, const std::string& name, Plan& plan) {
   const char* out_t = storageTypeOf(g.out_dtype);
   o << kConvertPrelude;
   o << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const " << in_t
-    << "* __restrict__ A, const " << in_t << "* __restrict__ B, " << out_t << "* __restrict__ C"
+ << "* __restrict__ A, const " << storageTypeOf(g.b_dtype) << "* __restrict__ B, " << out_t << "* __restrict__ C"
     << epilogueParams(g.epilogue) << ") {\n";
   o << "  const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;\n";
   o << "  if (idx >= " << g.batch * g.m * g.n << "ll) return;\n";
   o << "  const long long ni = idx % " << g.n << "ll;\n  const long long mi = (idx / " << g.n << "ll) % " << g.m
     << "ll;\n  const long long bi = idx / " << g.m * g.n << "ll;\n";
   o << "  const " << in_t << "* a = A + bi * " << g.a_stride_b << "ll + mi * " << g.a_stride_m << "ll;\n";
-  o << "  const " << in_t << "* b = B + bi * " << g.b_stride_b << "ll + ni * " << g.b_stride_n << "ll;\n";
+  o << "  const " << storageTypeOf(g.b_dtype) << "* b = B + bi * " << g.b_stride_b << "ll + ni * " << g.b_stride_n << "ll;\n";
   o << "  float acc = 0.0f;\n";
   o << "  for (long long k = 0; k < " << g.k << "ll; ++k) {\n";
   o << "    const float av = " << loadConv(g.in_dtype, "a[k * " + std::to_string(g.a_stride_k) + "ll]") << ";\n";
-  o << "    const float bv = " << loadConv(g.in_dtype, "b[k * " + std::to_string(g.b_stride_k) + "ll]") << ";\n";
+  o << "    const float bv = " <<  loadConv(g.b_dtype, "b[k * " + std::to_string(g.b_stride_k) + "ll]") << ";\n";
   o << "    const float prod = av * bv;\n    acc = acc + prod;\n  }\n";
   std::string result = emitEpilogueBody(g.epilogue, o, "  ", "acc", "bi", "mi", "ni", "");
   o << "  C[idx] = " << storeConv(g.out_dtype, result) << ";\n}\n";

@@ -77,7 +77,7 @@ struct GemmOp {
   int a_slot = -1, b_slot = -1, c_slot = -1;
   int64_t a_stride_b = 0, a_stride_m = 0, a_stride_k = 0;
   int64_t b_stride_b = 0, b_stride_k = 0, b_stride_n = 0;
-  DType in_dtype = DType::f32, out_dtype = DType::f32;
+  DType in_dtype = DType::f32, b_dtype = DType::f32, out_dtype = DType::f32;  // storage types of A, B, C
   Epilogue epilogue;
   bool tensor_core = false;      // tcgen05 path (bf16, tile-aligned) or SIMT k-serial path
 };
@@ -96,6 +96,10 @@ struct Slot {
   Role role = Temp;
   int io_index = -1;             // parameter index (Input) or output index (Output)
   size_t bytes = 0;
+  // Element type the buffer is stored in.  Inputs, outputs and constants use the program's type;
+  // a temporary holding a 16-bit-float value is stored as f32 unless a contraction reads it, so
+  // intermediate results between kernels are not rounded to 16 bits.
+  DType storage = DType::f32;
   uint32_t value = 0xffffffffu;  // program value the slot holds
   std::vector<uint8_t> payload;  // Constant: uploaded once at load time
 };
@@ -180,6 +184,7 @@ void emitGemm(const GemmOp& g, const std::string& name, Plan& plan, const Schedu
 void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan,
                    const ScheduleOverrides& o);
 bool tcgen05Ready();
+bool attentionReady();
 // Emits the C expression that evaluates an elementwise node from its operand expressions.
 std::string elementwiseExpr(const ENode& n, const std::string& a, const std::string& b,
                             const std::string& c, DType a_dtype);

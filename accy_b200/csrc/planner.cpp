@@ -56,6 +56,7 @@ class Planner {
       s.role = Slot::Input;
       s.io_index = static_cast<int>(i);
       s.bytes = P.typeOf(P.parameters[i]).byteCount();
+      s.storage = P.typeOf(P.parameters[i]).dtype;
       s.value = P.parameters[i];
       plan.slots.push_back(s);
       slot_of[P.parameters[i]] = static_cast<int>(plan.slots.size()) - 1;
@@ -70,6 +71,7 @@ class Planner {
       s.role = Slot::Output;
       s.io_index = static_cast<int>(j);
       s.bytes = P.typeOf(P.outputs[j]).byteCount();
+      s.storage = P.typeOf(P.outputs[j]).dtype;
       s.value = P.outputs[j];
       plan.slots.push_back(s);
       plan.output_slots[j] = static_cast<int>(plan.slots.size()) - 1;
@@ -114,10 +116,11 @@ class Planner {
     return s.str();
   }
 
-  int newSlot(Slot::Role role, size_t bytes, uint32_t value) {
+  int newSlot(Slot::Role role, size_t bytes, uint32_t value, DType storage) {
     Slot s;
     s.role = role;
     s.bytes = bytes;
+    s.storage = storage;
     s.value = value;
     plan.slots.push_back(s);
     return static_cast<int>(plan.slots.size()) - 1;
@@ -126,8 +129,13 @@ class Planner {
   // slot a kernel should write value v into
   int destinationSlot(uint32_t v) {
     if (is_output[v]) return out_slot_of[v];
-    return newSlot(Slot::Temp, P.typeOf(v).byteCount(), v);
+    const Type& ty = P.typeOf(v);
+    // 16-bit-float temporaries stay in f32 between kernels unless a contraction reads them
+    const bool widen = (ty.dtype == DType::bf16 || ty.dtype == DType::f16) && !narrow.count(v);
+    if (widen) return newSlot(Slot::Temp, ty.elementCount() * 4, v, DType::f32);
+    return newSlot(Slot::Temp, ty.byteCount(), v, ty.dtype);
   }
+  std::set<uint32_t> narrow;  // values that must keep their 16-bit storage (contraction operands)
 
   void planOutputRoot(uint32_t v) {
     const Operation& op = P.ops[v];
@@ -147,7 +155,7 @@ class Planner {
     const Operation& op = P.ops[v];
     switch (op.kind) {
       case Kind::constant: {
-        int s = newSlot(Slot::Constant, op.payload.size(), v);
+        int s = newSlot(Slot::Constant, op.payload.size(), v, op.result.dtype);
         plan.slots[s].payload = op.payload;
         slot_of[v] = s;
         if (is_output[v]) {
@@ -204,7 +212,7 @@ class Planner {
   int leafNode(Build& b, int slot, const Type& ty, const std::vector<int>& map) {
     LeafRef leaf;
     leaf.slot = slot;
-    leaf.dtype = ty.dtype;
+    leaf.dtype = plan.slots[slot].storage;
     leaf.strides.assign(b.extents.size(), 0);
     std::vector<int64_t> rm = rowMajorStrides(ty.dims);
     for (size_t i = 0; i < ty.dims.size(); ++i) {
@@ -552,6 +560,7 @@ class Planner {
       if (!outputRef(v, root_node, &ref))
         throw PlanError("fused region writes its result more than once per element (reduction over axes the result does not span)");
       ref.slot = destinationSlot(v);
+      ref.dtype = plan.slots[ref.slot].storage;
       c.leaves.push_back(ref);
       c.outputs.push_back({root_node, static_cast<int>(c.leaves.size()) - 1});
       out_values.push_back(v);
@@ -562,6 +571,7 @@ class Planner {
       LeafRef ref;
       if (!outputRef(cand.first, cand.second, &ref)) continue;
       ref.slot = destinationSlot(cand.first);
+      ref.dtype = plan.slots[ref.slot].storage;
       c.leaves.push_back(ref);
       c.outputs.push_back({cand.second, static_cast<int>(c.leaves.size()) - 1});
       out_values.push_back(cand.first);
@@ -657,7 +667,8 @@ class Planner {
     OperandView view;
     if (slot_of[cur] < 0 && (P.ops[cur].kind == Kind::parameter)) throw PlanError("parameter without slot");
     if (slot_of[cur] < 0) {
-      // computed operand: materialise the value itself in canonical order
+      // computed operand: materialise the value itself in canonical order, in its own 16-bit type
+      narrow.insert(v);
       view.slot = materialize(v);
       view.strides = rowMajorStrides(ty.dims);
       return view;
@@ -732,6 +743,7 @@ class Planner {
         break;
       }
       if (attempt == 1) throw PlanError("dot_general lhs layout cannot be expressed with strides");
+      narrow.insert(op.operands[0]);
       materialize(op.operands[0]);
     }
     for (int attempt = 0; attempt < 2; ++attempt) {
@@ -745,9 +757,11 @@ class Planner {
         break;
       }
       if (attempt == 1) throw PlanError("dot_general rhs layout cannot be expressed with strides");
+      narrow.insert(op.operands[1]);
       materialize(op.operands[1]);
     }
-    g.in_dtype = lt.dtype;
+    g.in_dtype = plan.slots[g.a_slot].storage;
+    g.b_dtype = plan.slots[g.b_slot].storage;
   }
 
   void planGemm(uint32_t dot, uint32_t root, Build* epilogue = nullptr, int result_node = -1) {
@@ -794,9 +808,10 @@ class Planner {
       }
     }
     g.c_slot = destinationSlot(root);
+    g.out_dtype = plan.slots[g.c_slot].storage;
     const bool aligned = g.m % 128 == 0 && g.n % 128 == 0 && g.k % 64 == 0 && g.a_stride_k == 1 &&
                          (g.b_stride_n == 1 || g.b_stride_k == 1);
-    g.tensor_core = g.in_dtype == DType::bf16 && aligned && !ov.force_simt_gemm && tcgen05Ready();
+    g.tensor_core = g.in_dtype == DType::bf16 && g.b_dtype == DType::bf16 && aligned && !ov.force_simt_gemm && tcgen05Ready();
     std::string name = nextName(g.tensor_core ? "gemm_tc" : "gemm_simt");
     summary << "gemm: " << name << " batch=" << g.batch << " m=" << g.m << " n=" << g.n << " k=" << g.k
             << " in=" << dtypeName(g.in_dtype) << " out=" << dtypeName(g.out_dtype)
@@ -1022,7 +1037,7 @@ class Planner {
                   (a.batch == 1 || (g1.a_stride_b == a.q_len * a.head_dim && g1.b_stride_b == a.k_len * a.head_dim &&
                                     g2.b_stride_b == a.k_len * a.head_dim));
     bool shape = a.head_dim == 128 && a.q_len % 128 == 0 && a.k_len % 128 == 0 && (!causal || a.q_len == a.k_len);
-    if (!layout || !shape || ov.force_simt_gemm || !tcgen05Ready()) return false;
+    if (!layout || !shape || ov.force_simt_gemm || !attentionReady()) return false;
     a.q_slot = g1.a_slot;
     a.k_slot = g1.b_slot;
     a.v_slot = g2.b_slot;

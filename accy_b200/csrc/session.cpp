@@ -67,6 +67,7 @@ struct accy_b200_session {
   CUcontext_t context = nullptr;
   CUstream_t stream = nullptr;
   int sm_count = 148;
+  CUdeviceptr_t status_word = 0;  // device int the tcgen05 kernels set when a bounded wait gives up
 
   void observe(const char* phase, uint64_t begin_ns) {
     if (observer) observer(observer_context, phase, nowNs() - begin_ns);
@@ -93,7 +94,23 @@ struct accy_b200_session {
     check(d->cuStreamCreate(&stream, 1 /* non-blocking */), "cuStreamCreate");
     int sms = 0;
     if (d->cuDeviceGetAttribute(&sms, 16 /* MULTIPROCESSOR_COUNT */, device) == 0 && sms > 0) sm_count = sms;
+    check(d->cuMemAlloc(&status_word, 256), "cuMemAlloc");
+    check(d->cuMemsetD8Async(status_word, 0, 256, stream), "cuMemsetD8Async");
+    check(d->cuStreamSynchronize(stream), "cuStreamSynchronize");
     device_ready = true;
+  }
+
+  // Reads the device status word after a synchronize: non-zero means a kernel gave up on a bounded
+  // wait (its results are invalid); the session is poisoned like after any failed launch.
+  void checkDeviceStatus(CUstream_t on) {
+    const DriverTable& d = driver();
+    int host = 0;
+    check(d.cuMemcpyDtoHAsync(&host, status_word, sizeof(host), on), "cuMemcpyDtoHAsync");
+    check(d.cuStreamSynchronize(on), "cuStreamSynchronize");
+    if (host != 0) {
+      poisoned = true;
+      throw StatusError{ACCY_B200_LAUNCH_FAILED, "a kernel gave up on a bounded wait (device status " + std::to_string(host) + ")"};
+    }
   }
 
   Entry& entryOf(uint64_t handle) {
@@ -175,7 +192,7 @@ struct accy_b200_session {
           ptrs[a] = map.get();
           maps.push_back(std::move(map));
         } else if (arg.is_slot) {
-          values[a] = e.bound[arg.slot];
+          values[a] = arg.slot == -2 ? status_word : e.bound[arg.slot];
           ptrs[a] = &values[a];
         } else {
           values[a] = arg.scalar;
@@ -267,6 +284,7 @@ void accy_b200_session_destroy(accy_b200_session* s) {
     if (s->device_ready) {
       const DriverTable& d = driver();
       d.cuCtxSetCurrent(s->context);
+      if (s->status_word) d.cuMemFree(s->status_word);
       if (s->stream) d.cuStreamDestroy(s->stream);
       d.cuDevicePrimaryCtxRelease(s->device);
     }
@@ -413,6 +431,7 @@ uint32_t accy_b200_session_invoke(accy_b200_session* s, uint64_t handle, const v
       s->poisoned = true;
       s->check(r, "cuStreamSynchronize");
     }
+    s->checkDeviceStatus(s->stream);
     s->observe("d2h_and_sync", t0);
   });
 }
@@ -443,11 +462,13 @@ uint32_t accy_b200_session_synchronize(accy_b200_session* s, void* stream) {
   return guarded(s, [&] {
     s->ensureDevice();
     const DriverTable& d = driver();
-    CUresult_t r = d.cuStreamSynchronize(stream ? static_cast<CUstream_t>(stream) : s->stream);
+    CUstream_t on = stream ? static_cast<CUstream_t>(stream) : s->stream;
+    CUresult_t r = d.cuStreamSynchronize(on);
     if (r != 0) {
       s->poisoned = true;
       s->check(r, "cuStreamSynchronize");
     }
+    s->checkDeviceStatus(on);
   });
 }
 

@@ -1,0 +1,380 @@
+"""Benchmark of the B200 execution target on the reference's headline configurations.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A "step" is one pass of a compiled program over one batch of synthetic input.  The default
+workload is the fused multi-reduction row program (softmax then layer-norm over
+f32[row=32768, col=4096], the HBM-bound configuration the headline GB/s figure is quoted on);
+`--workload mismatch|matmul|attention|mlp` selects the other benchmark programs.
+
+Prints ONE JSON line (rank 0).  `value` is whole-job throughput with inputs resident in HBM,
+timed with CUDA events on the launching stream, max over ranks; `e2e` is the same metric through
+the drop-in host-buffer call (`Session.invoke`: pinned host -> device copies, kernels and the
+device -> host read inside the timed region); `roofline` gives achieved algorithmic GB/s or
+TFLOP/s against the measured peak; `cpu_baseline` is the CPU restatement of the reference's
+`runCpu` arithmetic timed on this host (rank 0, N=1, bounded sample).
+
+With N > 1 (launched by torchrun, one rank per GPU) the program is sharded along its batch-like
+named axis with no exchange: every rank runs the full per-GPU workload on its own shard of an
+N-times larger global problem (weak scaling).  `--impl reference` times the CPU restatement on
+all host threads instead (rank 0 only).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, reasons, sm_max = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                sm_max = float(s[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, s[2:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": sm_max, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+WORKLOADS = {
+    # name: (metric, unit, bound, quantity-per-step key, scale)
+    "softmax_layernorm": ("fused_reduce_hbm_gbs", "GB/s", "hbm"),
+    "mismatch": ("fused_reduce_gpairs_per_s", "Gpair/s", "hbm"),
+    "matmul": ("matmul_tflops", "TFLOP/s", "tensor"),
+    "attention": ("attention_tflops", "TFLOP/s", "tensor"),
+    "mlp": ("mlp_tflops", "TFLOP/s", "tensor"),
+}
+
+
+def units_per_step(name, work):
+    if name == "softmax_layernorm":
+        return work["bytes"] / 1e9
+    if name == "mismatch":
+        return work["pairs"] / 1e9
+    return work["flops"] / 1e12
+
+
+def make_config(name, args):
+    from accy_b200 import configs
+    if args.small:
+        small = {"softmax_layernorm": lambda: configs.softmax_layernorm(2048, 4096),
+                 "mismatch": lambda: configs.mismatch(512, 8192),
+                 "matmul": lambda: configs.matmul(1024, 1024, 1024),
+                 "attention": lambda: configs.attention(1, 4, 1024, 128),
+                 "mlp": lambda: configs.mlp(1024, 1024, 2048)}
+        return small[name]()
+    return configs.BASELINE[name]()
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU legs (the only places that execute oracle/)
+# ---------------------------------------------------------------------------------------------
+def cpu_sample(name, cfg, inputs, threads, budget_s=15.0):
+    """Times the CPU restatement on a bounded sample of the workload; returns (units/s, cores, text)."""
+    import ctypes
+    from oracle import oracle
+    lib = oracle.lib()
+    lib.oracle_set_threads(threads)
+    c_size = ctypes.c_size_t
+
+    def ptr(a):
+        return a.ctypes.data_as(ctypes.c_void_p)
+
+    if name == "mismatch":
+        f, t, s = inputs
+        total = f.shape[0]
+        out = np.zeros(total, np.float32)
+
+        def run(n):
+            lib.oracle_mismatch_f32(ptr(f), ptr(t), ptr(s), ptr(out), c_size(total), c_size(t.shape[0]), c_size(0), c_size(n))
+        unit_of = lambda n: n * t.shape[0] / 1e9  # noqa: E731
+        label = "guesses"
+    elif name == "softmax_layernorm":
+        x = inputs[0]
+        total, cols = x.shape
+        out = np.zeros_like(x[:min(total, 4096)])
+
+        def run(n):
+            lib.oracle_softmax_layernorm_f32(ptr(x), ptr(out), c_size(total), c_size(cols), ctypes.c_float(1e-5), c_size(0), c_size(n))
+        unit_of = lambda n: 8.0 * n * cols / 1e9  # noqa: E731
+        total = min(total, 4096)
+        label = "rows"
+    elif name == "matmul":
+        a, b = inputs
+        total, k = a.shape
+        n_cols = b.shape[1]
+        out = np.zeros((min(total, 64), n_cols), np.float32)
+
+        def run(n):
+            lib.oracle_matmul_bf16(ptr(a), ptr(b), ptr(out), c_size(total), c_size(k), c_size(n_cols), c_size(0), c_size(n))
+        unit_of = lambda n: 2.0 * n * k * n_cols / 1e12  # noqa: E731
+        total = min(total, 64)
+        label = "rows of C"
+    elif name == "attention":
+        q, k, v = inputs
+        b_, h_, s_, d_ = q.shape
+        total = 1
+        out = np.zeros((1, s_, d_), np.float32)
+        scratch = np.zeros(max(1, threads) * s_, np.float32)
+        causal_pairs = s_ * (s_ + 1) / 2.0
+
+        def run(n):
+            lib.oracle_attention_bf16(ptr(q), ptr(k), ptr(v), ptr(out), c_size(b_ * h_), c_size(s_), c_size(s_), c_size(d_),
+                                      ctypes.c_float(float(1.0 / np.sqrt(d_))), ctypes.c_int(1), c_size(0), c_size(n), ptr(scratch))
+        unit_of = lambda n: 4.0 * d_ * causal_pairs * n / 1e12  # noqa: E731
+        label = "heads"
+    else:
+        x, w1, b1, w2, b2, g = inputs
+        tokens, d = x.shape
+        h = w1.shape[1]
+        total = min(tokens, 64)
+        out = np.zeros((total, d), np.float32)
+        hidden = np.zeros((total, h), np.float32)
+
+        def run(n):
+            lib.oracle_mlp_bf16(ptr(x), ptr(w1), ptr(b1), ptr(w2), ptr(b2), ptr(g), ptr(out), ptr(hidden), c_size(tokens),
+                                c_size(d), c_size(h), ctypes.c_float(1e-6), c_size(0), c_size(n))
+        unit_of = lambda n: 4.0 * n * d * h / 1e12  # noqa: E731
+        label = "tokens"
+    # grow the sample until it takes a measurable time, bounded by the budget
+    n = max(1, min(total, threads))
+    t0 = time.perf_counter()
+    run(n)
+    dt = time.perf_counter() - t0
+    while dt < min(budget_s, 10.0) / 4 and n < total:
+        n = min(total, max(n + 1, int(n * min(8.0, (budget_s / 2) / max(dt, 1e-4)))))
+        t0 = time.perf_counter()
+        run(n)
+        dt = time.perf_counter() - t0
+    return unit_of(n) / dt, threads, "%d of the workload's %s, %.1f s" % (n, label, dt), unit_of(n), dt
+
+
+def reference_arm(args, name, cfg):
+    """The reference's CPU implementation of the path (its restatement) on all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+    threads = oracle.lib().oracle_max_threads()
+    inputs = cfg.make_inputs()
+    metric, unit, _ = WORKLOADS[name]
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_sample(name, cfg, inputs, threads, budget_s=2.0)
+    total_units, total_time, sample = 0.0, 0.0, ""
+    for _ in range(args.steps):
+        _, _, sample, units, dt = cpu_sample(name, cfg, inputs, threads, budget_s=8.0)
+        total_units += units
+        total_time += dt
+    value = total_units / total_time
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total_time / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic",
+            "config": {"workload": name, "note": "CPU restatement of runCpu arithmetic, bounded sample per step"},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="softmax_layernorm", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures only; not a bench value)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    name = args.workload
+    cfg = make_config(name, args)
+    if args.impl == "reference":
+        reference_arm(args, name, cfg)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from accy_b200 import tensor
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the B200 target has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    metric, unit, bound = WORKLOADS[name]
+    peaks = load_peaks()
+
+    # every rank holds one full per-GPU workload: its shard of a world-times larger global problem
+    # along cfg.shard_axis (different seed per rank = different rows of the global input)
+    inputs = cfg.make_inputs()
+    program = cfg.program()
+    session = tensor.Session(device=local)
+    compiled = session.compile(program)
+    work = compiled.work()
+    d_in = [torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).cuda() for a in inputs]
+    out_desc = compiled.output_descriptors()
+    d_out = [torch.empty(d.byte_size, dtype=torch.uint8, device="cuda") for d in out_desc]
+    in_ptrs = [t.data_ptr() for t in d_in]
+    out_ptrs = [t.data_ptr() for t in d_out]
+    stream = torch.cuda.Stream()   # an explicit stream: its handle goes through the C ABI
+    torch.cuda.set_stream(stream)
+    io_bytes = sum(t.numel() * t.element_size() for t in d_in) + sum(t.numel() for t in d_out)
+    flush = None
+    if io_bytes < 256 * 1024 * 1024:
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+
+    def step():
+        session.invoke_device(compiled, in_ptrs, out_ptrs, stream.cuda_stream)
+
+    for _ in range(max(args.warmup, 3)):
+        if flush is not None:
+            flush.zero_()
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    wall0 = time.perf_counter()
+    for i in range(args.steps):
+        if flush is not None:
+            flush.zero_()
+        starts[i].record(stream)
+        step()
+        ends[i].record(stream)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - wall0
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    total_ms = float(sum(step_ms))
+    if world > 1:
+        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    units = units_per_step(name, cfg.work)
+    value = world * units * args.steps / (total_ms / 1e3)
+
+    # end to end through the drop-in host-buffer call, pinned host memory, copies inside the timing
+    e2e = None
+    if not args.no_e2e:
+        h_in = [torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).pin_memory() for a in inputs]
+        h_out = [torch.empty(d.byte_size, dtype=torch.uint8).pin_memory() for d in out_desc]
+        e2e_steps = max(2, min(args.steps, 5))
+        session.invoke(compiled, h_in, h_out)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            session.invoke(compiled, h_in, h_out)
+        e2e_s = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t.item())
+        e2e = {"value": world * units * e2e_steps / e2e_s, "unit": unit,
+               "h2d_bytes_per_step": int(sum(t.numel() * t.element_size() for t in h_in)),
+               "d2h_bytes_per_step": int(sum(t.numel() for t in h_out)), "ms_per_step": 1e3 * e2e_s / e2e_steps}
+
+    if rank == 0:
+        avg_ms = float(np.mean(step_ms))
+        if bound == "hbm":
+            achieved = cfg.work["bytes"] / 1e9 / (avg_ms / 1e3)
+            peak, peak_unit = peaks["hbm_gbs"], "GB/s"
+        else:
+            achieved = cfg.work["flops"] / 1e12 / (avg_ms / 1e3)
+            peak, peak_unit = peaks["bf16_tflops"], "TFLOP/s"
+        roofline = {"bound": bound, "achieved": achieved, "peak": peak, "unit": peak_unit, "frac": achieved / peak,
+                    "traffic": None, "peak_source": peaks["source"], "kernel_ms": avg_ms,
+                    "launches_per_step": work["launches"]}
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            v, cores, sample, _, _ = cpu_sample(name, cfg, inputs, 1, budget_s=15.0)
+            cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample}
+        line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic",
+                "config": {"workload": name, "specs": [repr(t) for t in program.input_types],
+                           "shard_axis": cfg.shard_axis, "parallelism": "shard%d" % world,
+                           "l2": "flushed between steps" if flush is not None else "inputs larger than L2",
+                           "small": bool(args.small), "plan": compiled.plan_summary().strip().split("\n")},
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": work["launches"] * args.steps,
+                "clocks": clocks, "wall_ms_per_step": 1e3 * wall / args.steps}
+        print(json.dumps(line))
+    session.deinit()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

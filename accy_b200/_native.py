@@ -74,6 +74,7 @@ PROTOTYPES = {
     "accy_b200_builder_finish": (c_u32, [c_p, P(c_u32), c_u32, P(P(ctypes.c_uint8)), P(c_size)]),
     "accy_b200_wire_reencode": (c_u32, [c_p, c_size, c_p, c_size, P(c_size), c_p, c_size]),
     "accy_b200_wire_describe": (c_u32, [c_p, c_size, c_p, c_size, P(c_size)]),
+    "accy_b200_mismatch_noalloc": (c_u32, [c_p, c_p, c_p, c_p, c_u64, c_u64, c_u32, c_p, c_p, c_size]),
     "accy_b200_test_use_fake_driver": (None, [ctypes.c_int32]),
     "accy_b200_test_fake_fail": (None, [c_str, ctypes.c_int32]),
     "accy_b200_test_fake_call_count": (c_u32, [c_str]),

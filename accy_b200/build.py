@@ -26,11 +26,25 @@ def needs_build():
     return os.path.getmtime(os.path.join(HERE, "..", "include", "accy_b200.h")) > built
 
 
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+CU_SOURCES = ["noalloc.cu"]   # fixed-function kernels compiled ahead of time by nvcc for sm_100a
+
+
 def build(force=False, verbose=False):
     if not force and not needs_build():
         return LIB
+    objects = []
+    for cu in CU_SOURCES:
+        obj = os.path.join(HERE, cu.replace(".cu", ".o"))
+        cmd = [os.path.join(CUDA_HOME, "bin", "nvcc"), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
+               "-std=c++17", "-Xcompiler", "-fPIC", "-c", os.path.join(CSRC, cu), "-o", obj]
+        if verbose:
+            print(" ".join(cmd))
+        subprocess.check_call(cmd)
+        objects.append(obj)
     cmd = ["g++", "-std=c++17", "-O2", "-g", "-fPIC", "-shared", "-Wall", "-Wextra", "-Wno-unused-parameter",
-           "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES] + ["-ldl", "-lpthread"]
+           "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES] + objects + [
+               "-L" + os.path.join(CUDA_HOME, "lib64"), "-lcudart_static", "-lrt", "-ldl", "-lpthread"]
     if verbose:
         print(" ".join(cmd))
     subprocess.check_call(cmd)

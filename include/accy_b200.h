@@ -174,6 +174,22 @@ uint32_t accy_b200_wire_reencode(const uint8_t* actp, size_t length, uint8_t* ou
 uint32_t accy_b200_wire_describe(const uint8_t* actp, size_t length, char* out, size_t capacity,
                                  size_t* out_length);
 
+/* ---- allocation-free entry point ----
+ * No counterpart in the reference.  For hosts that may not allocate device memory while running
+ * (a service whose pool owns the whole device, a real-time loop, a fixed stream schedule): the
+ * two-pass column-split "mismatch" reduction, out[g] = sum_p (sin(frequency[g]*time[p]) -
+ * sample[p])^2 in f32, with its partial sums kept in a 1 MiB array built into the library's device
+ * image instead of an allocated scratch buffer.  All four pointers are device pointers the caller
+ * already owns; `stream` is a CUstream/cudaStream_t (NULL = default stream); `splits` is the
+ * number of column splits wanted (clamped to the number of 4096-point chunks).  Limit:
+ * guesses * splits <= 262144, otherwise ACCY_B200_INVALID_BUFFER with a message in `error`.
+ * The call is asynchronous on `stream`.  Calls on one device share the array: issue them one
+ * after another, never overlapping.  The first call on a device looks up the array's device
+ * address; make it outside stream capture. */
+uint32_t accy_b200_mismatch_noalloc(const float* frequency, const float* time, const float* sample, float* out,
+                                    uint64_t guesses, uint64_t points, uint32_t splits, void* stream,
+                                    char* error, size_t error_capacity);
+
 /* ---- test support: a recording fake of the CUDA driver (the reference tests its CUDA backend
  * the same way, deps/lib/compiler/gpu/src/runtime/cuda/runtime.zig:643-1031) ---- */
 void accy_b200_test_use_fake_driver(int32_t enable);

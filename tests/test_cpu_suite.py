@@ -1,0 +1,369 @@
+"""CPU-side tests: recording rules, ACTP wire bytes, oracle known answers, fusion plans, kernel
+compilation for sm_100a (NVRTC, no device needed), C ABI exports and host logic on the fake driver."""
+import ctypes
+import json
+import os
+import re
+import struct
+
+import numpy as np
+import pytest
+
+from accy_b200 import _native, configs, tensor
+from accy_b200._native import lib
+from oracle import oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def golden_bytes():
+    with open(os.path.join(GOLDEN, "mismatch_2x16.actp"), "rb") as f:
+        return f.read()
+
+
+def known_answers():
+    with open(os.path.join(GOLDEN, "known_answers.json")) as f:
+        return json.load(f)
+
+
+# ---------------------------------------------------------------------------------------------
+# recording: named-axis rules and error names (examples/consumer/src/main.zig:230-249)
+# ---------------------------------------------------------------------------------------------
+def test_names_keep_guesses_and_points_apart_when_lengths_are_equal():
+    p = tensor.define("mismatch", [tensor.spec("f32", guess=16), tensor.spec("f32", point=16),
+                                   tensor.spec("f32", point=16)], configs.mismatch_body)
+    assert p.output_types[0].dims == [("guess", 16)]
+
+
+def test_different_lengths_are_refused_while_recording():
+    with pytest.raises(tensor.TensorError) as e:
+        tensor.define("mismatch", [tensor.spec("f32"), tensor.spec("f32", point=16), tensor.spec("f32", point=15)],
+                      configs.mismatch_body)
+    assert e.value.name == "AxisExtentMismatch"
+
+
+def test_builder_error_names():
+    b = tensor.Builder("t")
+    x = b.input("f32", a=2, b=3)
+    y = b.input("bf16", a=2)
+    for fn, name in [(lambda: x.add(y), "DTypeMismatch"), (lambda: x.sum("nope"), "AxisNotFound"),
+                     (lambda: x.sum(["a", "a"]), "DuplicateAxis"), (lambda: x.contract(y, "a"), "ContractDTypeMismatch"),
+                     (lambda: b.input("f32", **{"#x": 2}), "AxisNameReserved"), (lambda: x.rename("a", "b"), "DuplicateAxis"),
+                     (lambda: x.split("a", p=3, q=1), "SplitExtentMismatch")]:
+        with pytest.raises(tensor.TensorError) as e:
+            fn()
+        assert e.value.name == name, name
+    other = tensor.Builder("u")
+    with pytest.raises(tensor.TensorError) as e:
+        x.add(other.input("f32", a=2))
+    assert e.value.name == "CrossBuilderValue"
+    b.finish([x])
+    with pytest.raises(tensor.TensorError) as e:
+        x.neg()
+    assert e.value.name == "BuilderFinished"
+
+
+def test_union_order_alignment_and_contract_types():
+    b = tensor.Builder("t")
+    a = b.input("f32", n=4, m=3)
+    c = b.input("f32", m=3, k=5)
+    assert a.add(c).ty.dims == [("n", 4), ("m", 3), ("k", 5)]          # lhs dims first (algebra.zig:10-31)
+    assert c.add(a).ty.dims == [("m", 3), ("k", 5), ("n", 4)]
+    assert a.contract(c, "m").ty.dims == [("n", 4), ("k", 5)]
+    q = b.input("bf16", batch=2, head=3, seq=4, dim=8)
+    k = b.input("bf16", batch=2, head=3, key=5, dim=8)
+    assert q.contract(k, "dim").ty.dims == [("batch", 2), ("head", 3), ("seq", 4), ("key", 5)]
+    assert a.merge(["n", "m"], "nm").ty.dims == [("nm", 12)]
+    assert a.split("n", p=2, q=2).ty.dims == [("p", 2), ("q", 2), ("m", 3)]
+    assert a.mean("m").ty.dims == [("n", 4)]
+    assert a.compare("lt", a).ty.dtype == "i1"
+
+
+def test_recorded_op_lists_match_the_builder_rules():
+    """Independent decoder (oracle) sees the op list the reference's Builder would record."""
+    text = oracle.describe(configs.mismatch(8192, 65536).program().wire).splitlines()
+    kinds = [line.split()[1] for line in text[:-1]]
+    assert kinds == ["parameter", "parameter", "parameter", "broadcast_in_dim", "broadcast_in_dim", "binary", "unary",
+                     "broadcast_in_dim", "binary", "binary", "constant", "reduce"]
+    c2 = oracle.describe(configs.softmax_layernorm(8, 16).program().wire)
+    assert c2.count(" reduce ") == 4 and c2.count("broadcast_in_dim") == 7
+    c4 = oracle.describe(configs.attention(1, 2, 8, 4).program().wire)
+    assert c4.count("dot_general") == 2 and c4.count("transpose") == 1 and c4.count("iota") == 2
+
+
+# ---------------------------------------------------------------------------------------------
+# ACTP wire bytes
+# ---------------------------------------------------------------------------------------------
+def reencode(data):
+    buf = ctypes.create_string_buffer(len(data) + 4096)
+    n = ctypes.c_size_t()
+    err = ctypes.create_string_buffer(128)
+    src = ctypes.create_string_buffer(bytes(data), len(data))
+    status = lib.accy_b200_wire_reencode(ctypes.cast(src, ctypes.c_void_p), len(data), ctypes.cast(buf, ctypes.c_void_p),
+                                         len(buf), ctypes.byref(n), ctypes.cast(err, ctypes.c_void_p), 128)
+    return status, buf.raw[:n.value], err.value.decode()
+
+
+def test_encoder_matches_hand_assembled_golden_bytes():
+    program = configs.mismatch(2, 16).program()
+    assert program.wire == golden_bytes()
+
+
+def test_decode_reencode_round_trip_for_every_config():
+    for cfg in (configs.mismatch(4, 32), configs.softmax_layernorm(4, 32), configs.matmul(8, 8, 8),
+                configs.attention(1, 2, 8, 4), configs.mlp(4, 8, 16)):
+        wire = cfg.program().wire
+        status, again, _ = reencode(wire)
+        assert status == 0 and again == wire
+        assert oracle.describe(wire)  # the independent decoder accepts the same bytes
+
+
+def test_both_decoders_derive_the_same_types():
+    for cfg in (configs.softmax_layernorm(4, 32), configs.attention(1, 2, 8, 4), configs.mlp(4, 8, 16)):
+        wire = cfg.program().wire
+        buf = ctypes.create_string_buffer(1 << 16)
+        n = ctypes.c_size_t()
+        src = ctypes.create_string_buffer(wire, len(wire))
+        assert lib.accy_b200_wire_describe(ctypes.cast(src, ctypes.c_void_p), len(wire), ctypes.cast(buf, ctypes.c_void_p),
+                                           len(buf), ctypes.byref(n)) == 0
+        assert buf.value.decode() == oracle.describe(wire)
+
+
+def test_bad_bytes_are_refused_with_the_reference_error_names():
+    good = golden_bytes()
+    assert reencode(b"XXXX" + good[4:])[0::2] == (1, "BadMagic")
+    status, _, name = reencode(good[:4] + struct.pack("<I", 2) + good[8:])
+    assert (status, name) == (2, "UnsupportedVersion")
+    assert reencode(good[:-3])[0::2] == (1, "InvalidArtifact")            # ends early
+    assert reencode(good + b"\0")[0::2] == (1, "InvalidArtifact")         # trailing bytes
+    assert reencode(good[:-4] + struct.pack("<I", 99))[0::2] == (1, "InvalidReference")
+    # unknown kind code in the first operation
+    at = 4 + 4 + 4 + len("mismatch") + 4
+    assert reencode(good[:at] + struct.pack("<I", 77) + good[at + 4:])[0::2] == (1, "UnknownTag")
+
+
+# ---------------------------------------------------------------------------------------------
+# oracle pinned to the reference's shipped known answers
+# ---------------------------------------------------------------------------------------------
+def tone(points=16):
+    time = (0.25 * np.arange(points)).astype(np.float32)
+    return time, np.sin(3.0 * time.astype(np.float64)).astype(np.float32)
+
+
+def test_oracle_mismatch_known_answers():
+    ka = known_answers()["mismatch"]
+    time, sample = tone(ka["points"])
+    out = oracle.run(golden_bytes(), [np.array(ka["frequency"], np.float32), time, sample])[0]
+    for got, want, tol in zip(out, ka["value"], ka["abs_tolerance"]):
+        assert abs(float(got) - want) <= tol
+    # f64 restatement of the definition (main.zig:188-198), relative 1e-5 (main.zig:208)
+    exact = sum((np.sin(2.5 * float(t)) - float(s)) ** 2 for t, s in zip(time, sample))
+    assert abs(float(out[0]) - exact) <= 1e-5 * exact
+
+
+def test_oracle_eight_guesses_equal_eight_single_runs():
+    time, sample = tone()
+    starts = np.array([0.5, 1.0, 1.5, 2.0, 2.5, 3.5, 4.0, 4.5], np.float32)
+    together = oracle.run(configs.mismatch(8, 16).program().wire, [starts, time, sample])[0]
+    one = configs.mismatch(1, 16).program().wire
+    for start, value in zip(starts, together):
+        alone = oracle.run(one, [np.array([start], np.float32), time, sample])[0][0]
+        assert abs(alone - value) <= 1e-6 * abs(alone)                  # main.zig:226
+
+
+def test_oracle_dot_known_answer():
+    ka = known_answers()["dot_f32_2x3_3x2"]
+    program = tensor.define("dot", [tensor.spec("f32", m=2, k=3), tensor.spec("f32", k=3, n=2)], configs.matmul_body)
+    out = oracle.run(program.wire, [np.array(ka["lhs"], np.float32), np.array(ka["rhs"], np.float32)])[0]
+    assert out.reshape(-1).tolist() == ka["out"]
+
+
+def test_oracle_config_loops_agree_with_the_program_evaluator():
+    """The per-config C loops (used as the timed CPU baseline) compute what the generic evaluator does."""
+    o = oracle.lib()
+    size = ctypes.c_size_t
+
+    def ptr(a):
+        return a.ctypes.data_as(ctypes.c_void_p)
+    cfg = configs.mismatch(5, 300)
+    f, t, s = cfg.make_inputs()
+    out = np.zeros(5, np.float32)
+    o.oracle_mismatch_f32(ptr(f), ptr(t), ptr(s), ptr(out), size(5), size(300), size(0), size(5))
+    assert np.array_equal(out, oracle.run(cfg.program().wire, [f, t, s])[0])
+    cfg = configs.softmax_layernorm(6, 96)
+    x = cfg.make_inputs()[0]
+    out = np.zeros_like(x)
+    o.oracle_softmax_layernorm_f32(ptr(x), ptr(out), size(6), size(96), ctypes.c_float(1e-5), size(0), size(6))
+    assert np.array_equal(out, oracle.run(cfg.program().wire, [x])[0])
+    cfg = configs.attention(1, 2, 24, 16)
+    q, k, v = cfg.make_inputs()
+    out = np.zeros((2, 24, 16), np.float32)
+    scratch = np.zeros(24 * o.oracle_max_threads(), np.float32)
+    scale = float(configs.bf16_bits_to_f32(configs.f32_to_bf16_bits(np.array([0.25], np.float32)))[0])
+    o.oracle_attention_bf16(ptr(q), ptr(k), ptr(v), ptr(out), size(2), size(24), size(24), size(16),
+                            ctypes.c_float(scale), ctypes.c_int(1), size(0), size(2), ptr(scratch))
+    wide = configs.bf16_bits_to_f32(oracle.run(cfg.program().wire, [q, k, v], mode="wide")[0]).reshape(2, 24, 16)
+    assert np.max(np.abs(out - wide)) < 2e-2
+    cfg = configs.mlp(4, 16, 32)
+    ins = cfg.make_inputs()
+    out = np.zeros((4, 16), np.float32)
+    hidden = np.zeros((4, 32), np.float32)
+    o.oracle_mlp_bf16(*[ptr(a) for a in ins], ptr(out), ptr(hidden), size(4), size(16), size(32), ctypes.c_float(1e-6),
+                      size(0), size(4))
+    wide = configs.bf16_bits_to_f32(oracle.run(cfg.program().wire, ins, mode="wide")[0]).reshape(4, 16)
+    assert np.max(np.abs(out - wide)) < 3e-2
+
+
+# ---------------------------------------------------------------------------------------------
+# fusion plans and sm_100a compilation (NVRTC, compile-only session)
+# ---------------------------------------------------------------------------------------------
+def plan_of(session, cfg, **kw):
+    compiled = session.compile(cfg.program())
+    summary, work, kernels = compiled.plan_summary(), compiled.work(), compiled.kernels()
+    session.release(compiled)
+    return summary, work, kernels
+
+
+def test_mismatch_is_one_fused_reduction_kernel(cpu_session):
+    summary, work, kernels = plan_of(cpu_session, configs.mismatch())
+    assert work["launches"] == 1 and len(kernels) == 1
+    assert "rows=8192 cols=65536 reduces=1" in summary and "vec=4" in summary
+    assert work["bytes"] == 589824 and work["pairs"] == 536870912
+    assert "sinf(" in kernels[0][1] and "--fmad=false" in kernels[0][2]
+
+
+def test_few_guesses_use_the_deterministic_two_pass_combine(cpu_session):
+    summary, work, kernels = plan_of(cpu_session, configs.mismatch(4, 1 << 20))
+    assert work["launches"] == 2 and "splits=" in summary
+    assert [k[0].endswith("_combine") for k in kernels] == [False, True]
+    assert "atomic" not in kernels[0][1] and "atomic" not in kernels[1][1]
+
+
+def test_softmax_layernorm_is_one_row_kernel_with_the_row_in_registers(cpu_session):
+    summary, work, kernels = plan_of(cpu_session, configs.softmax_layernorm())
+    assert work["launches"] == 1 and "reduces=4" in summary and "chunks=1" in summary
+    assert work["bytes"] == 1073741824
+
+
+def test_matmul_uses_the_tcgen05_kernel(cpu_session):
+    summary, work, kernels = plan_of(cpu_session, configs.matmul())
+    assert "tcgen05" in summary and work["flops"] == 2.0 * 8192 ** 3
+    src = kernels[0][1]
+    assert "tcgen05.mma.cta_group::1.kind::f16" in src and "cp.async.bulk.tensor.3d" in src
+    assert "multicast" not in src
+
+
+def test_mlp_fuses_gelu_into_the_first_gemm_and_rmsnorm_into_one_row_kernel(cpu_session):
+    summary, work, kernels = plan_of(cpu_session, configs.mlp())
+    lines = summary.strip().split("\n")
+    assert len(lines) == 3 and work["launches"] == 3
+    assert "epilogue_nodes=16" in lines[0] and "tcgen05" in lines[0] and "tcgen05" in lines[1]
+    assert lines[2].startswith("row kernel") and "reduces=1" in lines[2]
+    assert "fast_tanh(" in kernels[0][1]
+
+
+def test_odd_shapes_fall_back_to_the_exact_order_simt_dot(cpu_session):
+    summary, _, kernels = plan_of(cpu_session, configs.matmul(96, 80, 72))
+    assert "simt" in summary and "acc = acc + prod" in kernels[0][1]
+
+
+def test_unsupported_programs_are_refused_not_emulated(cpu_session):
+    def body(b, a):
+        return a[0].pow(a[0])
+    program = tensor.define("ipow", [tensor.spec("i32", n=8)], body)
+    with pytest.raises(tensor.SessionError) as e:
+        cpu_session.compile(program)
+    assert e.value.name == "compile_failed"
+
+
+def test_compile_only_session_cannot_launch(cpu_session):
+    cfg = configs.mismatch(2, 16)
+    compiled = cpu_session.compile(cfg.program())
+    with pytest.raises(tensor.SessionError) as e:
+        cpu_session.invoke(compiled, cfg.make_inputs(), [np.zeros(2, np.float32)])
+    assert e.value.name == "launch_failed"
+    cpu_session.release(compiled)
+
+
+# ---------------------------------------------------------------------------------------------
+# C ABI surface and host logic (fake driver)
+# ---------------------------------------------------------------------------------------------
+def test_library_exports_every_symbol_the_header_declares():
+    with open(os.path.join(ROOT, "include", "accy_b200.h")) as f:
+        header = f.read()
+    declared = set(re.findall(r"\b(accy_b200_[a-z0-9_]+)\s*\(", header))
+    declared.discard("accy_b200_observer")
+    raw = ctypes.CDLL(_native.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(raw, name), name
+    assert declared == set(_native.PROTOTYPES), declared ^ set(_native.PROTOTYPES)
+
+
+@pytest.fixture
+def fake_driver():
+    lib.accy_b200_test_use_fake_driver(1)
+    yield
+    lib.accy_b200_test_use_fake_driver(0)
+
+
+def test_invoke_flow_on_the_fake_driver(fake_driver):
+    session = tensor.Session(device=0)
+    cfg = configs.mismatch(8, 16)
+    phases = []
+    session.set_observer(lambda phase, ns: phases.append(phase))
+    compiled = session.compile(cfg.program())
+    descs = compiled.input_descriptors() + compiled.output_descriptors()
+    assert [d.byte_size for d in descs] == [32, 64, 64, 32] and all(d.alignment == 256 for d in descs)
+    out = np.zeros(8, np.float32)
+    session.invoke(compiled, cfg.make_inputs(), [out])
+    assert lib.accy_b200_test_fake_call_count(b"cuLaunchKernel") == 1
+    assert lib.accy_b200_test_fake_call_count(b"cuMemcpyHtoDAsync") == 3
+    assert {"decode", "plan", "kernel_compile", "load", "h2d_enqueue", "launch_enqueue", "d2h_and_sync"} <= set(phases)
+    # exact sizes and no overlap (binding.zig:125-128, session.zig:176-178)
+    with pytest.raises(tensor.SessionError) as e:
+        session.invoke(compiled, cfg.make_inputs(), [np.zeros(7, np.float32)])
+    assert e.value.name == "invalid_buffer"
+    ins = cfg.make_inputs()
+    with pytest.raises(tensor.SessionError) as e:
+        session.invoke(compiled, ins, [ins[0]])
+    assert e.value.name == "invalid_buffer"
+    with pytest.raises(tensor.SessionError) as e:
+        session.invoke(compiled, ins[:2], [out])
+    assert e.value.name == "invalid_buffer"
+    # stale handles are refused after release (session.zig:58-64)
+    session.release(compiled)
+    with pytest.raises(tensor.SessionError) as e:
+        session.invoke(compiled, ins, [out])
+    assert e.value.name == "invalid_handle"
+    session.deinit()
+
+
+def test_failed_launch_poisons_the_session(fake_driver):
+    session = tensor.Session(device=0)
+    cfg = configs.mismatch(8, 16)
+    compiled = session.compile(cfg.program())
+    out = np.zeros(8, np.float32)
+    lib.accy_b200_test_fake_fail(b"cuLaunchKernel", 0)
+    with pytest.raises(tensor.SessionError) as e:
+        session.invoke(compiled, cfg.make_inputs(), [out])
+    assert e.value.name == "launch_failed" and "ILLEGAL_ADDRESS" in e.value.message
+    lib.accy_b200_test_fake_fail(b"cuLaunchKernel", -1)
+    with pytest.raises(tensor.SessionError) as e:
+        session.invoke(compiled, cfg.make_inputs(), [out])
+    assert "poisoned" in e.value.message
+    session.deinit()
+
+
+def test_at_most_64_programs_per_session(cpu_session):
+    held = []
+    wire = configs.mismatch(1, 4).program().wire
+    session = tensor.Session(device=-1)
+    for _ in range(64):
+        held.append(session.compile(wire))
+    with pytest.raises(tensor.SessionError) as e:
+        session.compile(wire)
+    assert e.value.name == "too_many_programs"
+    session.release(held.pop())
+    held.append(session.compile(wire))
+    session.deinit()

@@ -1,0 +1,372 @@
+// Fused scaled-dot-product attention for sm_100a: O = softmax(scale * Q K^T [+ causal mask]) V.
+//
+// Replaces the reference's flash-attention lowering (src/preparation/kernelization/lowering/
+// flash.zig:330-604: f32 only, head dim 64, non-causal, 32x32 tiles of scalar FMAs) and its
+// library SDPA (src/kernel/library/attention.zig:389-441) with a tcgen05 kernel for bf16,
+// head dim 128, optional causal mask, any number of leading batch axes:
+//   * one CTA owns 256 consecutive queries of one (batch, head) as two 128-row tiles; K/V blocks
+//     of 128 keys stream through a TMA ring and are shared by both tiles;
+//   * S = Q K^T and O += P V run on the tensor cores (tcgen05.mma, f32 accumulators in TMEM:
+//     S0, S1, O0, O1 = 4 x 128 columns); P is written back over S as bf16 and read by the second
+//     MMA straight from TMEM;
+//   * two softmax warpgroups (one per tile, one thread per query row, so row max and row sum need
+//     no shuffles) work in ping-pong with the MMA issuer: while one tile's softmax runs the
+//     tensor cores serve the other tile;
+//   * online softmax in f32 in the log2 domain (ex2.approx of fma(s, scale*log2e, -m)); O is only
+//     rescaled when a row's running max grows by more than 2^8, so the rescale through TMEM is rare;
+//   * causal programs skip key blocks above the diagonal and mask only the diagonal block.
+// Every mbarrier wait is bounded; on expiry the kernel sets the device status word and returns.
+#include <cmath>
+#include <sstream>
+
+#include "plan.hpp"
+
+namespace accy {
+
+extern const char* kConvertPrelude;
+extern const char* kTcPreludeShared;
+bool attentionReady() { return true; }
+
+namespace {
+
+void replaceAll(std::string& s, const std::string& from, const std::string& to) {
+  size_t at = 0;
+  while ((at = s.find(from, at)) != std::string::npos) {
+    s.replace(at, from.size(), to);
+    at += to.size();
+  }
+}
+
+const char* kAttentionTemplate = R"CUDA(
+#define SEQ_Q @SEQ_Q@
+#define SEQ_K @SEQ_K@
+#define BATCH @BATCH@
+#define CAUSAL @CAUSAL@
+#define HEAD_DIM 128
+#define TILE 128
+#define KV_STAGES 2
+#define TILE_BYTES (TILE * HEAD_DIM * 2)   // one 128 x 128 bf16 tile: two 64-wide boxes of 16 KB
+#define HALF_BYTES (TILE * 64 * 2)
+#define SCALE_LOG2 @SCALE_LOG2@f
+#define RESCALE_THRESHOLD 8.0f
+#ifndef INFINITY
+#define INFINITY __int_as_float(0x7f800000)
+#endif
+
+__device__ __forceinline__ void tc_st32(unsigned int taddr, const unsigned int* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+               "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+               :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                  "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                  "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                  "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+               : "memory");
+}
+
+extern "C" __global__ void __launch_bounds__(320, 1)
+@KERNEL@(const __grid_constant__ TensorMap map_q, const __grid_constant__ TensorMap map_k,
+         const __grid_constant__ TensorMap map_v, unsigned short* __restrict__ O, int* __restrict__ status) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((unsigned long long)smem_raw + 1023ull) & ~1023ull);
+  // layout: Q tile 0, Q tile 1, K stages, V stages, barriers
+  unsigned char* q_smem = smem;
+  unsigned char* k_smem = smem + 2 * TILE_BYTES;
+  unsigned char* v_smem = k_smem + KV_STAGES * TILE_BYTES;
+  unsigned long long* bars = (unsigned long long*)(v_smem + KV_STAGES * TILE_BYTES);
+  // bars: 0 q_full | 1..2 k_full | 3..4 k_empty | 5..6 v_full | 7..8 v_empty | 9..10 s_full | 11..12 p_full | 13..14 pv_done
+  unsigned int* tmem_holder = (unsigned int*)(bars + 16);
+  volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+  const unsigned int bar0 = smem_u32(bars);
+#define BAR(i) (bar0 + 8u * (i))
+  const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // work item: heaviest query pairs first
+  const int n_pairs = SEQ_Q / (2 * TILE);
+  const int pair = n_pairs - 1 - (int)(blockIdx.x / BATCH);
+  const int bh = (int)(blockIdx.x % BATCH);
+  const int q_row0 = pair * 2 * TILE;
+  // key blocks each tile attends to
+#if CAUSAL
+  const int n0 = q_row0 / TILE + 1, n1 = n0 + 1;
+#else
+  const int n0 = SEQ_K / TILE, n1 = n0;
+#endif
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 11; ++i) mbar_init(BAR(i), 1);
+    mbar_init(BAR(11), 4); mbar_init(BAR(12), 4);
+    mbar_init(BAR(13), 1); mbar_init(BAR(14), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(tmem_holder)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned int tmem_base = *tmem_holder;
+  // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t overwrites the first 64 columns of S_t
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      mbar_expect_tx(BAR(0), 2 * TILE_BYTES);
+      for (int t = 0; t < 2; ++t)
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(smem_u32(q_smem + t * TILE_BYTES + h * HALF_BYTES), &map_q, BAR(0), h * 64, q_row0 + t * TILE, bh);
+      bool ok = true;
+      for (int j = 0; ok && j < n1; ++j) {
+        const int stage = j % KV_STAGES;
+        const unsigned int ph = (unsigned int)((j / KV_STAGES) & 1);
+        if (!mbar_wait(BAR(3 + stage), ph ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(1 + stage), TILE_BYTES);
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(smem_u32(k_smem + stage * TILE_BYTES + h * HALF_BYTES), &map_k, BAR(1 + stage), h * 64, j * TILE, bh);
+        if (!mbar_wait(BAR(7 + stage), ph ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(5 + stage), TILE_BYTES);
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(smem_u32(v_smem + stage * TILE_BYTES + h * HALF_BYTES), &map_v, BAR(5 + stage), h * 64, j * TILE, bh);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      // S = Q K^T: A, B K-major, M = N = 128.  O += P V: A from TMEM, B = V with dim contiguous (N-major).
+      const unsigned int idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned int)(TILE >> 3) << 17) | ((unsigned int)(TILE >> 4) << 24);
+      const unsigned int idesc_o = idesc_s | (1u << 16);
+      bool ok = true;
+      auto issue_s = [&](int t, int j) {
+        const int stage = j % KV_STAGES;
+        const unsigned int qa = smem_u32(q_smem + t * TILE_BYTES), ka = smem_u32(k_smem + stage * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < HEAD_DIM / 16; ++k) {
+          const unsigned int off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          tc_mma_ss(tmem_base + t * TILE, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+        }
+        tc_commit(BAR(9 + t));
+      };
+      auto issue_pv = [&](int t, int j) {
+        const int stage = j % KV_STAGES;
+        const unsigned int va = smem_u32(v_smem + stage * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < TILE / 16; ++k)
+          tc_mma_ts(tmem_base + 2 * TILE + t * TILE, tmem_base + t * TILE + k * 8,
+                    smem_desc(va + k * 16 * 128, HALF_BYTES, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        tc_commit(BAR(13 + t));
+      };
+      auto wait_kv = [&](int base, int j) {
+        return mbar_wait(BAR(base + j % KV_STAGES), (unsigned int)((j / KV_STAGES) & 1), abort_flag);
+      };
+      ok = mbar_wait(BAR(0), 0, abort_flag) && wait_kv(1, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, 0);
+        issue_s(1, 0);
+        tc_commit(BAR(3));   // K stage 0 is free once both S MMAs have read it
+      }
+      for (int j = 0; ok && j < n1; ++j) {
+        const unsigned int ph = (unsigned int)(j & 1);
+        bool k_next = false;
+        if (j < n0) {
+          if (!(mbar_wait(BAR(11), ph, abort_flag) && wait_kv(5, j))) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(0, j);
+          if (j + 1 < n0) {
+            if (!wait_kv(1, j + 1)) { ok = false; break; }
+            k_next = true;
+            tc_fence_after();
+            issue_s(0, j + 1);
+          }
+        }
+        if (!(mbar_wait(BAR(12), ph, abort_flag) && wait_kv(5, j))) { ok = false; break; }
+        tc_fence_after();
+        issue_pv(1, j);
+        tc_commit(BAR(7 + j % KV_STAGES));   // V stage free
+        if (j + 1 < n1) {
+          if (!k_next && !wait_kv(1, j + 1)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(1, j + 1);
+          tc_commit(BAR(3 + (j + 1) % KV_STAGES));   // K stage free
+        }
+      }
+    }
+  } else {
+    // ---------------- softmax + correction + epilogue: warps 2..5 tile 0, warps 6..9 tile 1 ----------------
+    const int t = (warp - 2) >> 2;
+    const unsigned int quarter = warp & 3u;
+    const int row = (int)(quarter * 32 + lane);           // query row inside the tile
+    const int n_t = t == 0 ? n0 : n1;
+    const unsigned int lane_base = (quarter * 32u) << 16;
+    const unsigned int s_addr = tmem_base + lane_base + t * TILE;
+    const unsigned int o_addr = tmem_base + lane_base + 2 * TILE + t * TILE;
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+    for (int j = 0; ok && j < n_t; ++j) {
+      if (!mbar_wait(BAR(9 + t), (unsigned int)(j & 1), abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const bool diagonal = CAUSAL && (j == n_t - 1);
+      // pass 1: row max of the scaled scores
+      float m_blk = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        unsigned int r[32];
+        tc_ld32(s_addr + c * 32, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(r[i]) * SCALE_LOG2;
+          if (diagonal && (c * 32 + i) > row) x = -INFINITY;
+          m_blk = fmaxf(m_blk, x);
+        }
+      }
+      if (j == 0) {
+        m_run = m_blk;
+      } else {
+        const float m_new = fmaxf(m_run, m_blk);
+        const bool need = (m_new - m_run) > RESCALE_THRESHOLD;
+        if (__any_sync(0xffffffffu, need)) {
+          const float factor = need ? fast_exp2(m_run - m_new) : 1.0f;
+          if (need) { m_run = m_new; l_run *= factor; }
+          // O of this tile is up to date once the previous P V product has completed
+          if (!mbar_wait(BAR(13 + t), (unsigned int)((j - 1) & 1), abort_flag)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            unsigned int r[32];
+            tc_ld32(o_addr + c * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+            tc_st32(o_addr + c * 32, r);
+          }
+          tc_wait_st();
+        }
+      }
+      // pass 2: p = 2^(x - m), row sum, bf16 pairs written over S
+      float l_blk = 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        unsigned int packed[32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          unsigned int r[32];
+          tc_ld32(s_addr + c * 64 + h * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0 = fmaf(__uint_as_float(r[i]), SCALE_LOG2, -m_run);
+            float x1 = fmaf(__uint_as_float(r[i + 1]), SCALE_LOG2, -m_run);
+            const int col = c * 64 + h * 32 + i;
+            if (diagonal && col > row) x0 = -INFINITY;
+            if (diagonal && col + 1 > row) x1 = -INFINITY;
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            l_blk += p0 + p1;
+            packed[h * 16 + (i >> 1)] = pack_bf16(p0, p1);
+          }
+        }
+        // the S columns just read may be overwritten now: all 32 lanes of the warp have passed their loads
+        tc_st32(s_addr + c * 32, packed);
+      }
+      l_run += l_blk;
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(11 + t));
+    }
+    // epilogue: O / l -> bf16 -> global
+    if (ok && mbar_wait(BAR(13 + t), (unsigned int)((n_t - 1) & 1), abort_flag)) {
+      tc_fence_after();
+      const float inv = 1.0f / l_run;
+      unsigned short* orow = O + ((long long)bh * SEQ_Q + q_row0 + t * TILE + row) * HEAD_DIM;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        unsigned int r[32];
+        tc_ld32(o_addr + c * 32, r);
+        tc_wait_ld();
+        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          dst[q] = make_uint4(pack_bf16(__uint_as_float(r[q * 8 + 0]) * inv, __uint_as_float(r[q * 8 + 1]) * inv),
+                              pack_bf16(__uint_as_float(r[q * 8 + 2]) * inv, __uint_as_float(r[q * 8 + 3]) * inv),
+                              pack_bf16(__uint_as_float(r[q * 8 + 4]) * inv, __uint_as_float(r[q * 8 + 5]) * inv),
+                              pack_bf16(__uint_as_float(r[q * 8 + 6]) * inv, __uint_as_float(r[q * 8 + 7]) * inv));
+        }
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(status, 2);
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(512) : "memory");
+  }
+}
+)CUDA";
+
+}  // namespace
+
+void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, const ScheduleOverrides&) {
+  if (a.head_dim != 128 || a.q_len % 256 != 0 || a.k_len % 128 != 0)
+    throw PlanError("attention shape not covered by the fused kernel");
+  std::string src = std::string(kConvertPrelude) + kTcPreludeShared + kAttentionTemplate;
+  std::ostringstream scale;
+  scale.precision(9);
+  scale << std::scientific << static_cast<double>(a.scale) * 1.4426950408889634;
+  replaceAll(src, "@KERNEL@", name);
+  replaceAll(src, "@SEQ_Q@", std::to_string(a.q_len));
+  replaceAll(src, "@SEQ_K@", std::to_string(a.k_len));
+  replaceAll(src, "@BATCH@", std::to_string(a.batch));
+  replaceAll(src, "@CAUSAL@", a.causal ? "1" : "0");
+  replaceAll(src, "@SCALE_LOG2@", scale.str());
+  KernelSource ks;
+  ks.name = name;
+  ks.family = "attention";
+  ks.source = src;
+  plan.kernels.push_back(ks);
+
+  Launch l;
+  l.kernel = static_cast<int>(plan.kernels.size()) - 1;
+  const long long items = (a.q_len / 256) * a.batch;
+  if (items > 0x7fffffffll) throw PlanError("too many attention work items");
+  l.grid[0] = static_cast<uint32_t>(items);
+  l.block[0] = 320;
+  l.dynamic_smem = 6 * 32768 + 1024 + 256;
+  l.label = name;
+  auto map = [&](int slot, int64_t seq) {
+    KernelArg m;
+    m.is_slot = false;
+    m.tensor_map = true;
+    m.tma.slot = slot;
+    m.tma.rank = 3;
+    m.tma.elem_bytes = 2;
+    m.tma.swizzle = 3;
+    m.tma.dims[0] = 128;
+    m.tma.dims[1] = static_cast<uint64_t>(seq);
+    m.tma.dims[2] = static_cast<uint64_t>(a.batch);
+    m.tma.strides[0] = 128 * 2;
+    m.tma.strides[1] = static_cast<uint64_t>(seq) * 128 * 2;
+    m.tma.box[0] = 64;
+    m.tma.box[1] = 128;
+    m.tma.box[2] = 1;
+    return m;
+  };
+  l.args.push_back(map(a.q_slot, a.q_len));
+  l.args.push_back(map(a.k_slot, a.k_len));
+  l.args.push_back(map(a.v_slot, a.k_len));
+  KernelArg o;
+  o.slot = a.o_slot;
+  l.args.push_back(o);
+  KernelArg st;
+  st.slot = -2;
+  l.args.push_back(st);
+  plan.launches.push_back(l);
+}
+
+}  // namespace accy

@@ -25,7 +25,6 @@ std::string epilogueParams(const Epilogue& ep);
 extern const char* kConvertPrelude;
 
 bool tcgen05Ready() { return true; }
-bool attentionReady() { return false; }
 
 namespace {
 
@@ -414,8 +413,7 @@ void emitGemmTcgen05(const GemmOp& g, const std::string& name, Plan& plan, const
   plan.launches.push_back(l);
 }
 
-void emitAttention(const AttentionOp&, const std::string&, Plan&, const ScheduleOverrides&) {
-  throw PlanError("tcgen05 attention emitter not available");
-}
+// the tcgen05 building blocks, shared with the attention kernel (emit_attn.cpp)
+const char* kTcPreludeShared = kTcPrelude;
 
 }  // namespace accy

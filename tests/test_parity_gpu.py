@@ -98,7 +98,8 @@ def test_dot_f32_known_answer(gpu_session):
 
 
 @pytest.mark.parametrize("batch,head,seq,dim,causal", [(1, 1, 48, 32, False), (1, 2, 64, 32, True), (2, 2, 256, 128, True),
-                                                        (1, 2, 256, 128, False)])
+                                                        (1, 2, 256, 128, False), (1, 3, 1024, 128, True),
+                                                        (2, 1, 512, 128, False), (1, 1, 2048, 128, True)])
 def test_attention_matches_f32_reference(gpu_session, batch, head, seq, dim, causal):
     cfg = configs.attention(batch, head, seq, dim, causal)
     inputs = cfg.make_inputs()

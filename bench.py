@@ -114,11 +114,12 @@ def units_per_step(name, work):
 def make_config(name, args):
     from accy_b200 import configs
     if args.small:
-        small = {"softmax_layernorm": lambda: configs.softmax_layernorm(2048, 4096),
-                 "mismatch": lambda: configs.mismatch(512, 8192),
-                 "matmul": lambda: configs.matmul(1024, 1024, 1024),
-                 "attention": lambda: configs.attention(1, 4, 1024, 128),
-                 "mlp": lambda: configs.mlp(1024, 1024, 2048)}
+        # profiling sizes: the same kernels, inputs still larger than L2 where the kernel is HBM-bound
+        small = {"softmax_layernorm": lambda: configs.softmax_layernorm(8192, 4096),
+                 "mismatch": lambda: configs.mismatch(1024, 65536),
+                 "matmul": lambda: configs.matmul(4096, 4096, 4096),
+                 "attention": lambda: configs.attention(1, 16, 4096, 128),
+                 "mlp": lambda: configs.mlp(4096, 4096, 4096)}
         return small[name]()
     return configs.BASELINE[name]()
 
@@ -246,6 +247,8 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures only; not a bench value)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--tpr", type=int, default=0, help="schedule override: threads per row (experiments)")
+    ap.add_argument("--vpt", type=int, default=0, help="schedule override: vectors per thread (experiments)")
     args = ap.parse_args()
     name = args.workload
     cfg = make_config(name, args)
@@ -272,7 +275,7 @@ def main():
     # along cfg.shard_axis (different seed per rank = different rows of the global input)
     inputs = cfg.make_inputs()
     program = cfg.program()
-    session = tensor.Session(device=local)
+    session = tensor.Session(device=local, threads_per_row=args.tpr, vectors_per_thread=args.vpt)
     compiled = session.compile(program)
     work = compiled.work()
     d_in = [torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).cuda() for a in inputs]

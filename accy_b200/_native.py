@@ -18,7 +18,8 @@ P = ctypes.POINTER
 class Options(ctypes.Structure):
     _fields_ = [("device", ctypes.c_int32), ("threads_per_row", ctypes.c_int32),
                 ("vectors_per_thread", ctypes.c_int32), ("column_splits", ctypes.c_int32),
-                ("force_simt_gemm", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
+                ("force_simt_gemm", ctypes.c_int32), ("row_min_blocks", ctypes.c_int32),
+                ("reserved", ctypes.c_int32 * 2)]
 
 
 class Descriptor(ctypes.Structure):

@@ -149,6 +149,7 @@ struct ScheduleOverrides {
   int vectors_per_thread = 0;
   int column_splits = 0;
   int force_simt_gemm = 0;
+  int row_min_blocks = 0;
   int sm_count = 148;
 };
 
@@ -176,6 +177,7 @@ struct RowSchedule {
   int vpt = 1;         // vector accesses per thread per chunk
   int64_t chunks = 1;  // chunk iterations per row (1 = the whole row lives in registers)
   int splits = 1;      // CTAs sharing one row (deterministic two-pass combine when > 1)
+  int min_blocks = 0;  // resident CTAs per SM asked of the compiler (caps registers), 0 = no request
 };
 RowSchedule chooseRowSchedule(const Cluster& c, const ScheduleOverrides& o);
 void emitRowKernels(const Cluster& c, const RowSchedule& s, const std::string& name, Plan& plan,

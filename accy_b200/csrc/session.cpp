@@ -313,6 +313,7 @@ uint32_t accy_b200_session_compile(accy_b200_session* s, const uint8_t* actp, si
     ov.vectors_per_thread = s->options.vectors_per_thread;
     ov.column_splits = s->options.column_splits;
     ov.force_simt_gemm = s->options.force_simt_gemm;
+    ov.row_min_blocks = s->options.row_min_blocks;
     ov.sm_count = s->sm_count;
     fresh.plan = planProgram(fresh.program, ov);
     s->observe("plan", t0);

@@ -61,7 +61,8 @@ typedef struct accy_b200_options {
   int32_t vectors_per_thread; /* schedule override, 0 = automatic */
   int32_t column_splits;      /* schedule override, 0 = automatic */
   int32_t force_simt_gemm;    /* 1 = never use the tcgen05 kernels (exact k-serial order) */
-  int32_t reserved[3];
+  int32_t row_min_blocks;     /* schedule override: resident CTAs per SM requested of row kernels, 0 = automatic */
+  int32_t reserved[2];
 } accy_b200_options;
 
 /* One input or output slot: session.zig:66-74 (Descriptor). */

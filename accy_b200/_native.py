@@ -19,7 +19,7 @@ class Options(ctypes.Structure):
     _fields_ = [("device", ctypes.c_int32), ("threads_per_row", ctypes.c_int32),
                 ("vectors_per_thread", ctypes.c_int32), ("column_splits", ctypes.c_int32),
                 ("force_simt_gemm", ctypes.c_int32), ("row_min_blocks", ctypes.c_int32),
-                ("reserved", ctypes.c_int32 * 2)]
+                ("single_shot_invoke", ctypes.c_int32), ("reserved", ctypes.c_int32 * 1)]
 
 
 class Descriptor(ctypes.Structure):
@@ -74,6 +74,7 @@ PROTOTYPES = {
     "accy_b200_builder_value_type": (c_u32, [c_p, c_u32, P(Descriptor)]),
     "accy_b200_builder_finish": (c_u32, [c_p, P(c_u32), c_u32, P(P(ctypes.c_uint8)), P(c_size)]),
     "accy_b200_wire_reencode": (c_u32, [c_p, c_size, c_p, c_size, P(c_size), c_p, c_size]),
+    "accy_b200_wire_shard": (c_u32, [c_p, c_size, c_str, ctypes.c_int64, c_p, c_size, P(c_size), P(c_u32), c_p, c_size]),
     "accy_b200_wire_describe": (c_u32, [c_p, c_size, c_p, c_size, P(c_size)]),
     "accy_b200_mismatch_noalloc": (c_u32, [c_p, c_p, c_p, c_p, c_u64, c_u64, c_u32, c_p, c_p, c_size]),
     "accy_b200_test_use_fake_driver": (None, [ctypes.c_int32]),

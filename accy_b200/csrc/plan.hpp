@@ -169,6 +169,18 @@ struct PlanError : std::runtime_error {
 
 Plan planProgram(const Program& program, const ScheduleOverrides& overrides);
 
+// Sharding along a named axis (shard.cpp).
+struct ShardInfo {
+  std::string axis;
+  int64_t extent = -1;          // the axis' extent in the program
+  bool shardable = false;
+  bool partial_sum = false;     // pieces produce partial sums of every output (add them up)
+  std::vector<uint32_t> partial_outputs;
+  std::string reason;           // why not, when !shardable
+};
+ShardInfo analyseShardAxis(const Program& program, const std::string& axis);
+Program shardProgram(const Program& program, const std::string& axis, int64_t extent);
+
 // code emission (emit_row.cpp, emit_gemm.cpp)
 struct RowSchedule {
   int tpr = 32;        // threads cooperating on one row

@@ -45,6 +45,18 @@ struct Entry {
   std::vector<std::vector<std::string>> names;  // descriptor name storage
   CUevent_t ev_begin = nullptr, ev_end = nullptr;
   bool timed = false;
+  // Chunked host invoke: the program re-recorded for a slice of its outermost batch-like axis,
+  // loaded three times (three lanes = three streams with their own buffers) so that the copy in
+  // of chunk i+1, the kernels of chunk i and the copy out of chunk i-1 overlap.
+  struct Pipeline {
+    bool tried = false, ready = false;
+    int chunks = 1;
+    std::vector<std::unique_ptr<Entry>> lanes;
+    std::vector<CUstream_t> streams;
+    std::vector<bool> input_sharded;           // per parameter: carries the chunked axis
+    std::vector<CUdeviceptr_t> shared_inputs;  // per parameter: one device copy of a replicated input
+    CUevent_t shared_ready = nullptr;
+  } pipeline;
 };
 
 struct StatusError {
@@ -113,6 +125,179 @@ struct accy_b200_session {
     }
   }
 
+  // plan the entry's program and compile every kernel of the plan to an sm_100a cubin
+  void planAndCompile(Entry& x) {
+    uint64_t t0 = nowNs();
+    ScheduleOverrides ov;
+    ov.threads_per_row = options.threads_per_row;
+    ov.vectors_per_thread = options.vectors_per_thread;
+    ov.column_splits = options.column_splits;
+    ov.force_simt_gemm = options.force_simt_gemm;
+    ov.row_min_blocks = options.row_min_blocks;
+    ov.sm_count = sm_count;
+    x.plan = planProgram(x.program, ov);
+    observe("plan", t0);
+    t0 = nowNs();
+    x.kernels.resize(x.plan.kernels.size());
+    for (size_t k = 0; k < x.plan.kernels.size(); ++k) {
+      const KernelSource& ks = x.plan.kernels[k];
+      std::string log;
+      try {
+        x.kernels[k].cubin = compileToCubin(ks.source, ks.name, ks.options, &log);
+      } catch (const std::exception& ex) {
+        throw StatusError{ACCY_B200_COMPILE_FAILED, ex.what()};
+      }
+      std::ostringstream opts;
+      for (const std::string& o : ks.options) opts << o << " ";
+      x.kernels[k].options = opts.str();
+    }
+    observe("kernel_compile", t0);
+  }
+
+  void allocateStaging(Entry& x) {
+    if (x.staging_ready) return;
+    const DriverTable& d = driver();
+    for (int slot : x.plan.input_slots)
+      if (!x.owned[slot]) check(d.cuMemAlloc(&x.owned[slot], x.plan.slots[slot].bytes ? x.plan.slots[slot].bytes : 1), "cuMemAlloc");
+    for (int slot : x.plan.output_slots)
+      if (!x.owned[slot]) check(d.cuMemAlloc(&x.owned[slot], x.plan.slots[slot].bytes ? x.plan.slots[slot].bytes : 1), "cuMemAlloc");
+    x.staging_ready = true;
+  }
+
+  // Builds the chunked variant of a program for the host-buffer invoke, when the program's
+  // outermost output axis can be cut into independent pieces and there is enough data for the
+  // overlap to pay.  Any failure simply leaves the single-shot path in place.
+  void buildPipeline(Entry& e) {
+    Entry::Pipeline& P = e.pipeline;
+    P.tried = true;
+    size_t io_bytes = 0;
+    for (int slot : e.plan.input_slots) io_bytes += e.plan.slots[slot].bytes;
+    for (int slot : e.plan.output_slots) io_bytes += e.plan.slots[slot].bytes;
+    if (io_bytes < (64u << 20) || e.program.outputs.empty()) return;
+    const Type& out0 = e.program.typeOf(e.program.outputs[0]);
+    if (out0.rank() == 0) return;
+    const std::string axis = out0.dims[0].name;
+    ShardInfo info = analyseShardAxis(e.program, axis);
+    if (!info.shardable || info.partial_sum) return;
+    int chunks = 16;
+    while (chunks > 1 && (info.extent % chunks != 0 || io_bytes / chunks < (16u << 20))) chunks /= 2;
+    if (chunks < 2) return;
+    try {
+      Entry piece;
+      piece.program = shardProgram(e.program, axis, info.extent / chunks);
+      planAndCompile(piece);
+      const DriverTable& d = driver();
+      for (int lane = 0; lane < 3; ++lane) {
+        auto x = std::make_unique<Entry>();
+        x->program = piece.program;
+        x->plan = piece.plan;
+        x->kernels.resize(piece.kernels.size());
+        for (size_t k = 0; k < piece.kernels.size(); ++k) {
+          x->kernels[k].cubin = piece.kernels[k].cubin;
+          x->kernels[k].options = piece.kernels[k].options;
+        }
+        x->live = true;
+        P.lanes.push_back(std::move(x));
+        loadKernels(*P.lanes.back());
+        CUstream_t st = nullptr;
+        check(d.cuStreamCreate(&st, 1), "cuStreamCreate");
+        P.streams.push_back(st);
+      }
+      P.input_sharded.assign(e.program.parameters.size(), false);
+      P.shared_inputs.assign(e.program.parameters.size(), 0);
+      for (size_t i = 0; i < e.program.parameters.size(); ++i) {
+        const Type& t = e.program.typeOf(e.program.parameters[i]);
+        P.input_sharded[i] = findDim(t.dims, axis) == 0;
+        if (!P.input_sharded[i]) check(d.cuMemAlloc(&P.shared_inputs[i], t.byteCount() ? t.byteCount() : 1), "cuMemAlloc");
+      }
+      // lanes own chunk-sized staging for the sliced inputs and for every output
+      for (auto& lane : P.lanes) {
+        for (size_t i = 0; i < e.program.parameters.size(); ++i) {
+          int slot = lane->plan.input_slots[i];
+          if (P.input_sharded[i]) check(d.cuMemAlloc(&lane->owned[slot], lane->plan.slots[slot].bytes ? lane->plan.slots[slot].bytes : 1), "cuMemAlloc");
+        }
+        for (int slot : lane->plan.output_slots)
+          check(d.cuMemAlloc(&lane->owned[slot], lane->plan.slots[slot].bytes ? lane->plan.slots[slot].bytes : 1), "cuMemAlloc");
+        lane->staging_ready = true;
+      }
+      check(d.cuEventCreate(&P.shared_ready, 2 /* disable timing */), "cuEventCreate");
+      P.chunks = chunks;
+      P.ready = true;
+    } catch (const StatusError&) {
+      dropPipeline(e);
+    } catch (const std::exception&) {
+      dropPipeline(e);
+    }
+  }
+
+  void dropPipeline(Entry& e) {
+    Entry::Pipeline& P = e.pipeline;
+    if (device_ready) {
+      const DriverTable& d = driver();
+      for (auto& lane : P.lanes)
+        if (lane) unload(*lane);
+      for (CUstream_t st : P.streams)
+        if (st) d.cuStreamDestroy(st);
+      for (CUdeviceptr_t p : P.shared_inputs)
+        if (p) d.cuMemFree(p);
+      if (P.shared_ready) d.cuEventDestroy(P.shared_ready);
+    }
+    bool tried = P.tried;
+    P = Entry::Pipeline{};
+    P.tried = tried;
+  }
+
+  void runPipelined(Entry& e, const void* const* inputs, void* const* outputs) {
+    if (poisoned) throw StatusError{ACCY_B200_LAUNCH_FAILED, "session is poisoned by an earlier failed launch"};
+    Entry::Pipeline& P = e.pipeline;
+    const DriverTable& d = driver();
+    uint64_t t0 = nowNs();
+    for (size_t i = 0; i < P.input_sharded.size(); ++i) {
+      if (P.input_sharded[i]) continue;
+      size_t bytes = e.plan.slots[e.plan.input_slots[i]].bytes;
+      if (bytes) check(d.cuMemcpyHtoDAsync(P.shared_inputs[i], inputs[i], bytes, P.streams[0]), "cuMemcpyHtoDAsync");
+    }
+    check(d.cuEventRecord(P.shared_ready, P.streams[0]), "cuEventRecord");
+    for (size_t lane = 1; lane < P.streams.size(); ++lane)
+      check(d.cuStreamWaitEvent(P.streams[lane], P.shared_ready, 0), "cuStreamWaitEvent");
+    for (int c = 0; c < P.chunks; ++c) {
+      Entry& x = *P.lanes[c % P.lanes.size()];
+      CUstream_t st = P.streams[c % P.streams.size()];
+      x.bound = x.owned;
+      for (size_t i = 0; i < P.input_sharded.size(); ++i) {
+        int slot = x.plan.input_slots[i];
+        if (!P.input_sharded[i]) {
+          x.bound[slot] = P.shared_inputs[i];
+          continue;
+        }
+        size_t bytes = x.plan.slots[slot].bytes;
+        if (bytes)
+          check(d.cuMemcpyHtoDAsync(x.owned[slot], static_cast<const char*>(inputs[i]) + static_cast<size_t>(c) * bytes, bytes, st),
+                "cuMemcpyHtoDAsync");
+      }
+      launchAll(x, st, false);
+      for (size_t j = 0; j < x.plan.output_slots.size(); ++j) {
+        int slot = x.plan.output_slots[j];
+        size_t bytes = x.plan.slots[slot].bytes;
+        if (bytes)
+          check(d.cuMemcpyDtoHAsync(static_cast<char*>(outputs[j]) + static_cast<size_t>(c) * bytes, x.owned[slot], bytes, st),
+                "cuMemcpyDtoHAsync");
+      }
+    }
+    observe("pipeline_enqueue", t0);
+    t0 = nowNs();
+    for (CUstream_t st : P.streams) {
+      CUresult_t r = d.cuStreamSynchronize(st);
+      if (r != 0) {
+        poisoned = true;
+        check(r, "cuStreamSynchronize");
+      }
+    }
+    checkDeviceStatus(P.streams[0]);
+    e.timed = false;
+    observe("pipeline_sync", t0);
+  }
+
   Entry& entryOf(uint64_t handle) {
     uint32_t index = static_cast<uint32_t>(handle & 0xffffffffu);
     uint32_t generation = static_cast<uint32_t>(handle >> 32);
@@ -154,6 +339,7 @@ struct accy_b200_session {
   }
 
   void unload(Entry& e) {
+    dropPipeline(e);
     if (device_ready) {
       const DriverTable& d = driver();
       d.cuCtxSetCurrent(context);
@@ -308,30 +494,7 @@ uint32_t accy_b200_session_compile(accy_b200_session* s, const uint8_t* actp, si
     s->observe("decode", t0);
     if (s->options.device >= 0) s->ensureDevice();
     t0 = nowNs();
-    ScheduleOverrides ov;
-    ov.threads_per_row = s->options.threads_per_row;
-    ov.vectors_per_thread = s->options.vectors_per_thread;
-    ov.column_splits = s->options.column_splits;
-    ov.force_simt_gemm = s->options.force_simt_gemm;
-    ov.row_min_blocks = s->options.row_min_blocks;
-    ov.sm_count = s->sm_count;
-    fresh.plan = planProgram(fresh.program, ov);
-    s->observe("plan", t0);
-    t0 = nowNs();
-    fresh.kernels.resize(fresh.plan.kernels.size());
-    for (size_t k = 0; k < fresh.plan.kernels.size(); ++k) {
-      const KernelSource& ks = fresh.plan.kernels[k];
-      std::string log;
-      try {
-        fresh.kernels[k].cubin = compileToCubin(ks.source, ks.name, ks.options, &log);
-      } catch (const std::exception& ex) {
-        throw StatusError{ACCY_B200_COMPILE_FAILED, ex.what()};
-      }
-      std::ostringstream opts;
-      for (const std::string& o : ks.options) opts << o << " ";
-      fresh.kernels[k].options = opts.str();
-    }
-    s->observe("kernel_compile", t0);
+    s->planAndCompile(fresh);
     fresh.names.resize(fresh.program.parameters.size() + fresh.program.outputs.size());
     e = std::move(fresh);
     e.live = true;
@@ -402,14 +565,13 @@ uint32_t accy_b200_session_invoke(accy_b200_session* s, uint64_t handle, const v
     s->ensureDevice();
     const DriverTable& d = driver();
     s->check(d.cuCtxSetCurrent(s->context), "cuCtxSetCurrent");
-    if (!e.staging_ready) {
-      // device-resident staging buffers are created once and kept with the program
-      for (int slot : e.plan.input_slots)
-        if (!e.owned[slot]) s->check(d.cuMemAlloc(&e.owned[slot], e.plan.slots[slot].bytes ? e.plan.slots[slot].bytes : 1), "cuMemAlloc");
-      for (int slot : e.plan.output_slots)
-        if (!e.owned[slot]) s->check(d.cuMemAlloc(&e.owned[slot], e.plan.slots[slot].bytes ? e.plan.slots[slot].bytes : 1), "cuMemAlloc");
-      e.staging_ready = true;
+    if (!e.pipeline.tried && !s->options.single_shot_invoke) s->buildPipeline(e);
+    if (e.pipeline.ready) {
+      s->runPipelined(e, inputs, outputs);
+      return;
     }
+    // device-resident staging buffers are created once and kept with the program
+    s->allocateStaging(e);
     e.bound = e.owned;
     uint64_t t0 = nowNs();
     for (uint32_t i = 0; i < input_count; ++i) {
@@ -713,6 +875,33 @@ uint32_t accy_b200_wire_reencode(const uint8_t* actp, size_t length, uint8_t* ou
       error_name[error_capacity - 1] = '\0';
     }
     return std::string(e.what()) == "UnsupportedVersion" ? ACCY_B200_UNSUPPORTED_VERSION : ACCY_B200_INVALID_PROGRAM;
+  }
+}
+
+uint32_t accy_b200_wire_shard(const uint8_t* actp, size_t length, const char* axis, int64_t extent, uint8_t* out,
+                              size_t capacity, size_t* out_length, uint32_t* partial_sum, char* error,
+                              size_t error_capacity) {
+  auto fail = [&](uint32_t status, const char* what) {
+    if (error && error_capacity) {
+      std::strncpy(error, what, error_capacity - 1);
+      error[error_capacity - 1] = '\0';
+    }
+    return status;
+  };
+  try {
+    Program p = decodeProgram(actp, length);
+    ShardInfo info = analyseShardAxis(p, axis ? axis : "");
+    Program piece = shardProgram(p, axis ? axis : "", extent);
+    std::vector<uint8_t> bytes = encodeProgram(piece);
+    if (out_length) *out_length = bytes.size();
+    if (partial_sum) *partial_sum = info.partial_sum ? 1u : 0u;
+    if (bytes.size() > capacity) return fail(ACCY_B200_INVALID_BUFFER, "output buffer too small");
+    std::memcpy(out, bytes.data(), bytes.size());
+    return ACCY_B200_OK;
+  } catch (const PlanError& e) {
+    return fail(ACCY_B200_COMPILE_FAILED, e.what());
+  } catch (const std::exception& e) {
+    return fail(ACCY_B200_INVALID_PROGRAM, e.what());
   }
 }
 

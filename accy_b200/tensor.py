@@ -288,6 +288,33 @@ def define(name, specs, body):
     return Program(name, wire, input_types, output_types)
 
 
+def shard_program(program, axis, extent):
+    """Re-records `program` with `extent` for the named axis so it can run as independent pieces
+    (one rank per GPU, or one chunk at a time).  Returns (piece, partial_sum): when partial_sum
+    is True every output of a piece is a partial sum over the axis and the pieces must be added
+    (one all-reduce); otherwise piece i's outputs are rows [i*extent, (i+1)*extent) of the full
+    outputs.  Raises SessionError("compile_failed") when an operation mixes values across the axis."""
+    wire = program.wire if isinstance(program, Program) else bytes(program)
+    src = ctypes.create_string_buffer(wire, len(wire))
+    out = ctypes.create_string_buffer(len(wire) + 65536)
+    n = ctypes.c_size_t()
+    partial = ctypes.c_uint32()
+    err = ctypes.create_string_buffer(512)
+    status = lib.accy_b200_wire_shard(ctypes.cast(src, ctypes.c_void_p), len(wire), axis.encode(), int(extent),
+                                      ctypes.cast(out, ctypes.c_void_p), len(out), ctypes.byref(n), ctypes.byref(partial),
+                                      ctypes.cast(err, ctypes.c_void_p), 512)
+    if status:
+        raise SessionError(status, err.value.decode(errors="replace"))
+    piece_wire = out.raw[:n.value]
+
+    def resize(types):
+        return [Type(t.dtype, [(name, extent if name == axis else e) for name, e in t.dims]) for t in types]
+    name = program.name if isinstance(program, Program) else "shard"
+    inputs = resize(program.input_types) if isinstance(program, Program) else []
+    outputs = resize(program.output_types) if isinstance(program, Program) else []
+    return Program(name, piece_wire, inputs, outputs), bool(partial.value)
+
+
 # ---------------------------------------------------------------------------------------------
 # execution
 # ---------------------------------------------------------------------------------------------

@@ -68,11 +68,15 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6:
-                self.samples.append(parts)
+                self.samples.append((time.perf_counter(), parts))
 
-    def stop(self):
+    def count_since(self, t0):
+        return sum(1 for t, _ in self.samples if t >= t0)
+
+    def stop(self, t0, t1, how):
+        """Summarises the samples that arrived between t0 and t1 (perf_counter times under load)."""
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "sampled": "nvidia-smi unavailable"}
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -80,7 +84,9 @@ class ClockSampler:
             self.proc.kill()
         mhz, reasons, sm_max = [], set(), None
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        for t, s in self.samples:
+            if t < t0 or t > t1:
+                continue
             try:
                 mhz.append(float(s[0]))
                 sm_max = float(s[1])
@@ -90,7 +96,7 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": sm_max, "reasons": sorted(reasons),
-                "samples": len(mhz)}
+                "samples": len(mhz), "sampled": how}
 
 
 WORKLOADS = {
@@ -103,6 +109,14 @@ WORKLOADS = {
 }
 
 
+def _size_args(name, cfg):
+    """(label, extent) pairs that rebuild a config of the same size with another seed"""
+    dims = {n: e for s in cfg.specs for n, e in s.dims}
+    order = {"mismatch": ["guess", "point"], "softmax_layernorm": ["row", "col"], "matmul": ["m", "n", "k"],
+             "attention": ["batch", "head", "seq", "dim"], "mlp": ["token", "d", "h"]}[name]
+    return [(n, dims[n]) for n in order]
+
+
 def units_per_step(name, work):
     if name == "softmax_layernorm":
         return work["bytes"] / 1e9
@@ -111,8 +125,12 @@ def units_per_step(name, work):
     return work["flops"] / 1e12
 
 
-def make_config(name, args):
+def make_config(name, args, seed_offset=0):
     from accy_b200 import configs
+    if seed_offset:
+        base = {"mismatch": 0, "softmax_layernorm": 1, "matmul": 2, "attention": 3, "mlp": 4}[name]
+        sizes = make_config(name, args)
+        return configs.BASELINE[name](*[e for _, e in _size_args(name, sizes)], seed=base + 1000 * seed_offset)
     if args.small:
         # profiling sizes: the same kernels, inputs still larger than L2 where the kernel is HBM-bound
         small = {"softmax_layernorm": lambda: configs.softmax_layernorm(8192, 4096),
@@ -274,6 +292,8 @@ def main():
 
     # every rank holds one full per-GPU workload: its shard of a world-times larger global problem
     # along cfg.shard_axis (different seed per rank = different rows of the global input)
+    if world > 1:
+        cfg = make_config(name, args, seed_offset=rank)   # every rank holds different rows of the global input
     inputs = cfg.make_inputs()
     program = cfg.program()
     session = tensor.Session(device=local, threads_per_row=args.tpr, vectors_per_thread=args.vpt,
@@ -295,6 +315,10 @@ def main():
     def step():
         session.invoke_device(compiled, in_ptrs, out_ptrs, stream.cuda_stream)
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()   # nvidia-smi needs a few hundred ms before its first sample
+    load_t0 = time.perf_counter()
     for _ in range(max(args.warmup, 3)):
         if flush is not None:
             flush.zero_()
@@ -302,9 +326,6 @@ def main():
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     torch.cuda.synchronize()
@@ -319,7 +340,22 @@ def main():
     wall = time.perf_counter() - wall0
     if world > 1:
         dist.barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = None
+    if rank == 0:
+        # The timed region is often shorter than one nvidia-smi period.  When it holds no sample,
+        # the same step keeps running right after it until a few samples exist, and those are
+        # reported (the GPU never idles in between, so they show the clocks of the timed region).
+        load_t1 = time.perf_counter()
+        how = "during warm-up and timed steps"
+        if sampler.proc and sampler.count_since(load_t0) < 3:
+            how = "same step repeated right after the timed steps"
+            deadline = time.perf_counter() + 2.5
+            while sampler.count_since(load_t0) < 4 and time.perf_counter() < deadline:
+                for _ in range(8):
+                    step()
+                torch.cuda.synchronize()
+            load_t1 = time.perf_counter()
+        clocks = sampler.stop(load_t0, load_t1, how)
     step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
     total_ms = float(sum(step_ms))
     if world > 1:

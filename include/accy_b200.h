@@ -62,7 +62,8 @@ typedef struct accy_b200_options {
   int32_t column_splits;      /* schedule override, 0 = automatic */
   int32_t force_simt_gemm;    /* 1 = never use the tcgen05 kernels (exact k-serial order) */
   int32_t row_min_blocks;     /* schedule override: resident CTAs per SM requested of row kernels, 0 = automatic */
-  int32_t reserved[2];
+  int32_t single_shot_invoke; /* 1 = host-buffer invoke never streams the program through the GPU in chunks */
+  int32_t reserved[1];
 } accy_b200_options;
 
 /* One input or output slot: session.zig:66-74 (Descriptor). */
@@ -171,6 +172,14 @@ uint32_t accy_b200_builder_finish(accy_b200_builder* b, const uint32_t* outputs,
 /* ---- wire: decode + re-encode (round-trip check of foreign ACTP bytes) ---- */
 uint32_t accy_b200_wire_reencode(const uint8_t* actp, size_t length, uint8_t* out, size_t capacity,
                                  size_t* out_length, char* error_name, size_t error_capacity);
+/* Re-records a program with extent `extent` for the named axis, for running it as independent
+ * pieces (one per GPU, or one per chunk).  No counterpart in the reference, which runs on one
+ * device.  Refused (COMPILE_FAILED, reason in `error`) when an operation mixes values across the
+ * axis.  *partial_sum = 1 when the program's outputs are sums over the axis: the pieces' outputs
+ * must then be added (one all-reduce). */
+uint32_t accy_b200_wire_shard(const uint8_t* actp, size_t length, const char* axis, int64_t extent, uint8_t* out,
+                              size_t capacity, size_t* out_length, uint32_t* partial_sum, char* error,
+                              size_t error_capacity);
 /* Operation list of decoded bytes as text, one op per line: "id kind dtype[name=extent,...] ...". */
 uint32_t accy_b200_wire_describe(const uint8_t* actp, size_t length, char* out, size_t capacity,
                                  size_t* out_length);

@@ -367,3 +367,41 @@ def test_at_most_64_programs_per_session(cpu_session):
     session.release(held.pop())
     held.append(session.compile(wire))
     session.deinit()
+
+
+def test_large_host_invokes_stream_through_the_device_in_chunks(fake_driver):
+    """Programs with enough data are re-recorded for a slice of their outermost axis and run chunk
+    by chunk on three streams; replicated inputs are copied once."""
+    session = tensor.Session(device=0)
+    cfg = configs.softmax_layernorm(4096, 4096)           # 64 MiB in + 64 MiB out
+    compiled = session.compile(cfg.program())
+    x = np.zeros((4096, 4096), np.float32)
+    out = np.zeros_like(x)
+    before = lib.accy_b200_test_fake_call_count(b"cuLaunchKernel")
+    copies = lib.accy_b200_test_fake_call_count(b"cuMemcpyHtoDAsync")
+    session.invoke(compiled, [x], [out])
+    assert lib.accy_b200_test_fake_call_count(b"cuLaunchKernel") - before == 8
+    assert lib.accy_b200_test_fake_call_count(b"cuMemcpyHtoDAsync") - copies == 8
+    session.deinit()
+    single = tensor.Session(device=0, single_shot_invoke=1)
+    compiled = single.compile(cfg.program())
+    before = lib.accy_b200_test_fake_call_count(b"cuLaunchKernel")
+    single.invoke(compiled, [x], [out])
+    assert lib.accy_b200_test_fake_call_count(b"cuLaunchKernel") - before == 1
+    single.deinit()
+
+
+def test_shard_program_rules():
+    piece, partial = tensor.shard_program(configs.mismatch(8, 64).program(), "guess", 4)
+    assert not partial and piece.wire == configs.mismatch(4, 64).program().wire
+    piece, partial = tensor.shard_program(configs.mismatch(8, 64).program(), "point", 16)
+    assert partial and piece.input_types[1].dims == [("point", 16)]
+    for cfg, axis in [(configs.softmax_layernorm(8, 32), "col"), (configs.matmul(16, 8, 8), "k"),
+                      (configs.attention(4, 2, 8, 4), "seq")]:
+        with pytest.raises(tensor.SessionError) as e:
+            tensor.shard_program(cfg.program(), axis, 2)
+        assert e.value.name == "compile_failed"
+    for cfg, axis in [(configs.softmax_layernorm(8, 32), "row"), (configs.matmul(16, 8, 8), "m"),
+                      (configs.attention(4, 2, 8, 4), "batch"), (configs.mlp(8, 8, 16), "token")]:
+        piece, partial = tensor.shard_program(cfg.program(), axis, 2)
+        assert not partial and piece.output_types[0].dims[0] == (axis, 2)

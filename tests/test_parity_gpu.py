@@ -152,3 +152,21 @@ def test_mismatch_full_size_sample(gpu_session):
                                      inputs[2].ctypes.data_as(ctypes.c_void_p), exact.ctypes.data_as(ctypes.c_void_p),
                                      ctypes.c_size_t(16), ctypes.c_size_t(65536))
     assert rel_err(got[:16], exact, 1e-6) < 1e-5
+
+
+@pytest.mark.parametrize("make", [lambda: configs.softmax_layernorm(8192, 4096), lambda: configs.mlp(4096, 2048, 4096),
+                                  lambda: configs.attention(8, 4, 1024, 128)])
+def test_chunked_host_invoke_equals_single_shot(make):
+    """The streamed (chunked, three-lane) host invoke returns the same bytes as one launch over the whole input."""
+    cfg = make()
+    inputs = cfg.make_inputs()
+    results = []
+    for single in (0, 1):
+        session = tensor.Session(device=0, single_shot_invoke=single)
+        compiled = session.compile(cfg.program())
+        outs = [np.empty(d.byte_size, np.uint8) for d in compiled.output_descriptors()]
+        session.invoke(compiled, inputs, outs)
+        session.invoke(compiled, inputs, outs)   # buffers are reused across invocations
+        results.append(outs[0].copy())
+        session.deinit()
+    assert np.array_equal(results[0], results[1])

@@ -168,12 +168,11 @@ def cpu_sample(name, cfg, inputs, threads, budget_s=15.0):
     elif name == "softmax_layernorm":
         x = inputs[0]
         total, cols = x.shape
-        out = np.zeros_like(x[:min(total, 4096)])
+        out = np.zeros_like(x)
 
         def run(n):
             lib.oracle_softmax_layernorm_f32(ptr(x), ptr(out), c_size(total), c_size(cols), ctypes.c_float(1e-5), c_size(0), c_size(n))
         unit_of = lambda n: 8.0 * n * cols / 1e9  # noqa: E731
-        total = min(total, 4096)
         label = "rows"
     elif name == "matmul":
         a, b = inputs
@@ -293,9 +292,20 @@ def main():
     # every rank holds one full per-GPU workload: its shard of a world-times larger global problem
     # along cfg.shard_axis (different seed per rank = different rows of the global input)
     if world > 1:
-        cfg = make_config(name, args, seed_offset=rank)   # every rank holds different rows of the global input
+        # The global problem is `world` times larger along the shard axis; the shard planner cuts the
+        # recorded global program into one piece per rank (no exchange), and every rank generates
+        # its own block of the global input (a different seed per rank).
+        from accy_b200 import configs, shard
+        sizes = dict(_size_args(name, cfg))
+        sizes[cfg.shard_axis] *= world
+        global_cfg = configs.BASELINE[name](*[sizes[n] for n, _ in _size_args(name, cfg)])
+        plan = shard.ShardPlan(global_cfg.program(), cfg.shard_axis, world)
+        assert not plan.partial_sum
+        cfg = make_config(name, args, seed_offset=rank)
+        program = plan.piece
+    else:
+        program = cfg.program()
     inputs = cfg.make_inputs()
-    program = cfg.program()
     session = tensor.Session(device=local, threads_per_row=args.tpr, vectors_per_thread=args.vpt,
                              row_min_blocks=args.min_blocks)
     compiled = session.compile(program)

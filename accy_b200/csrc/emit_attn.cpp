@@ -208,19 +208,35 @@ extern "C" __global__ void __launch_bounds__(320, 1)
       if (!mbar_wait(BAR(9 + t), (unsigned int)(j & 1), abort_flag)) { ok = false; break; }
       tc_fence_after();
       const bool diagonal = CAUSAL && (j == n_t - 1);
-      // pass 1: row max of the scaled scores
-      float m_blk = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        unsigned int r[32];
-        tc_ld32(s_addr + c * 32, r);
+      // pass 1: row max.  The scale is positive, so the max is taken over the raw scores and
+      // scaled once; the four loads are in flight together and four chains fold them.
+      float m_blk;
+      {
+        unsigned int r0[32], r1[32], r2[32], r3[32];
+        tc_ld32(s_addr, r0);
+        tc_ld32(s_addr + 32, r1);
+        tc_ld32(s_addr + 64, r2);
+        tc_ld32(s_addr + 96, r3);
         tc_wait_ld();
+        float a = -INFINITY, b = -INFINITY, c = -INFINITY, d = -INFINITY;
+        if (diagonal) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(r[i]) * SCALE_LOG2;
-          if (diagonal && (c * 32 + i) > row) x = -INFINITY;
-          m_blk = fmaxf(m_blk, x);
+          for (int i = 0; i < 32; ++i) {
+            a = fmaxf(a, i > row ? -INFINITY : __uint_as_float(r0[i]));
+            b = fmaxf(b, 32 + i > row ? -INFINITY : __uint_as_float(r1[i]));
+            c = fmaxf(c, 64 + i > row ? -INFINITY : __uint_as_float(r2[i]));
+            d = fmaxf(d, 96 + i > row ? -INFINITY : __uint_as_float(r3[i]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            a = fmaxf(a, __uint_as_float(r0[i]));
+            b = fmaxf(b, __uint_as_float(r1[i]));
+            c = fmaxf(c, __uint_as_float(r2[i]));
+            d = fmaxf(d, __uint_as_float(r3[i]));
+          }
         }
+        m_blk = fmaxf(fmaxf(a, b), fmaxf(c, d)) * SCALE_LOG2;
       }
       if (j == 0) {
         m_run = m_blk;
@@ -245,31 +261,44 @@ extern "C" __global__ void __launch_bounds__(320, 1)
           tc_wait_st();
         }
       }
-      // pass 2: p = 2^(x - m), row sum, bf16 pairs written over S
-      float l_blk = 0.0f;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        unsigned int packed[32];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          unsigned int r[32];
-          tc_ld32(s_addr + c * 64 + h * 32, r);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0 = fmaf(__uint_as_float(r[i]), SCALE_LOG2, -m_run);
-            float x1 = fmaf(__uint_as_float(r[i + 1]), SCALE_LOG2, -m_run);
-            const int col = c * 64 + h * 32 + i;
-            if (diagonal && col > row) x0 = -INFINITY;
-            if (diagonal && col + 1 > row) x1 = -INFINITY;
-            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-            l_blk += p0 + p1;
-            packed[h * 16 + (i >> 1)] = pack_bf16(p0, p1);
-          }
-        }
-        // the S columns just read may be overwritten now: all 32 lanes of the warp have passed their loads
-        tc_st32(s_addr + c * 32, packed);
+      // pass 2: p = 2^(x - m), row sum, bf16 pairs written over S (64 columns at a time: the
+      // columns a thread overwrites are columns it has already read)
+      float l_a = 0.0f, l_b = 0.0f;
+#define SOFTMAX_HALF(C, MASKED)                                                              \
+      {                                                                                      \
+        unsigned int ra[32], rb[32], packed[32];                                             \
+        tc_ld32(s_addr + (C) * 64, ra);                                                      \
+        tc_ld32(s_addr + (C) * 64 + 32, rb);                                                 \
+        tc_wait_ld();                                                                        \
+        _Pragma("unroll")                                                                    \
+        for (int i = 0; i < 32; i += 2) {                                                    \
+          float x0 = fmaf(__uint_as_float(ra[i]), SCALE_LOG2, -m_run);                       \
+          float x1 = fmaf(__uint_as_float(ra[i + 1]), SCALE_LOG2, -m_run);                   \
+          float y0 = fmaf(__uint_as_float(rb[i]), SCALE_LOG2, -m_run);                       \
+          float y1 = fmaf(__uint_as_float(rb[i + 1]), SCALE_LOG2, -m_run);                   \
+          if (MASKED) {                                                                      \
+            const int col = (C) * 64 + i;                                                    \
+            if (col > row) x0 = -INFINITY;                                                   \
+            if (col + 1 > row) x1 = -INFINITY;                                               \
+            if (col + 32 > row) y0 = -INFINITY;                                              \
+            if (col + 33 > row) y1 = -INFINITY;                                              \
+          }                                                                                  \
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), q0 = fast_exp2(y0), q1 = fast_exp2(y1); \
+          l_a += p0 + p1;                                                                    \
+          l_b += q0 + q1;                                                                    \
+          packed[i >> 1] = pack_bf16(p0, p1);                                                \
+          packed[16 + (i >> 1)] = pack_bf16(q0, q1);                                         \
+        }                                                                                    \
+        tc_st32(s_addr + (C) * 32, packed);                                                  \
       }
+      if (diagonal) {
+        SOFTMAX_HALF(0, true)
+        SOFTMAX_HALF(1, true)
+      } else {
+        SOFTMAX_HALF(0, false)
+        SOFTMAX_HALF(1, false)
+      }
+      const float l_blk = l_a + l_b;
       l_run += l_blk;
       tc_wait_st();
       tc_fence_before();

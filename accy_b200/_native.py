@@ -19,7 +19,7 @@ class Options(ctypes.Structure):
     _fields_ = [("device", ctypes.c_int32), ("threads_per_row", ctypes.c_int32),
                 ("vectors_per_thread", ctypes.c_int32), ("column_splits", ctypes.c_int32),
                 ("force_simt_gemm", ctypes.c_int32), ("row_min_blocks", ctypes.c_int32),
-                ("single_shot_invoke", ctypes.c_int32), ("reserved", ctypes.c_int32 * 1)]
+                ("single_shot_invoke", ctypes.c_int32), ("attention_poly", ctypes.c_int32)]
 
 
 class Descriptor(ctypes.Structure):

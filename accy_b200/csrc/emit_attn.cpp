@@ -49,9 +49,38 @@ const char* kAttentionTemplate = R"CUDA(
 #define HALF_BYTES (TILE * 64 * 2)
 #define SCALE_LOG2 @SCALE_LOG2@f
 #define RESCALE_THRESHOLD 8.0f
+#define POLY_SHARE @POLY_SHARE@   // of every 8 pairs in the second half of a 64-column group
 #ifndef INFINITY
 #define INFINITY __int_as_float(0x7f800000)
 #endif
+
+// packed f32x2 helpers (two IEEE f32 operations per instruction)
+__device__ __forceinline__ unsigned long long pk2(float lo, float hi) { unsigned long long r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ unsigned long long pk2u(unsigned int lo, unsigned int hi) { unsigned long long r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi)); return r; }
+__device__ __forceinline__ void upk2(unsigned long long v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) { unsigned long long r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ unsigned long long sub2(unsigned long long a, unsigned long long b) { unsigned long long r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) { unsigned long long r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
+// 2^x for a pair of values on the FMA pipe: x = n + f with n = round(x), f in [-1/2, 1/2];
+// 2^f by a degree-4 polynomial (error below 2^-14, the result is rounded to bf16 afterwards),
+// then n is added to the exponent field.  x is clamped at -126 so the exponent cannot wrap.
+__device__ __forceinline__ void poly_exp2_pair(unsigned long long x2, float& out0, float& out1) {
+  float x0, x1;
+  upk2(x2, x0, x1);
+  x2 = pk2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+  const unsigned long long magic2 = pk2(12582912.0f, 12582912.0f);
+  const unsigned long long t2 = add2(x2, magic2);
+  const unsigned long long f2 = sub2(x2, sub2(t2, magic2));
+  unsigned long long p2 = fma2(f2, pk2(0.00961813f, 0.00961813f), pk2(0.05550411f, 0.05550411f));
+  p2 = fma2(p2, f2, pk2(0.24022651f, 0.24022651f));
+  p2 = fma2(p2, f2, pk2(0.69314718f, 0.69314718f));
+  p2 = fma2(p2, f2, pk2(1.0f, 1.0f));
+  float p0, p1, t0, t1;
+  upk2(p2, p0, p1);
+  upk2(t2, t0, t1);
+  out0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  out1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
 
 __device__ __forceinline__ void tc_st32(unsigned int taddr, const unsigned int* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -291,12 +320,44 @@ extern "C" __global__ void __launch_bounds__(320, 1)
         }                                                                                    \
         tc_st32(s_addr + (C) * 32, packed);                                                  \
       }
+      // unmasked blocks: the scale-and-shift is a packed FMA, and a fixed share of the
+      // exponentials (POLY_SHARE of every 8 pairs) runs on the FMA pipe to relieve the
+      // special-function unit, which otherwise limits the kernel as much as the tensor cores do
+#define SOFTMAX_HALF_FAST(C)                                                                 \
+      {                                                                                      \
+        unsigned int ra[32], rb[32], packed[32];                                             \
+        tc_ld32(s_addr + (C) * 64, ra);                                                      \
+        tc_ld32(s_addr + (C) * 64 + 32, rb);                                                 \
+        tc_wait_ld();                                                                        \
+        _Pragma("unroll")                                                                    \
+        for (int i = 0; i < 32; i += 2) {                                                    \
+          const unsigned long long x2 = fma2(pk2u(ra[i], ra[i + 1]), c2, nm2);               \
+          const unsigned long long y2 = fma2(pk2u(rb[i], rb[i + 1]), c2, nm2);               \
+          float p0, p1, q0, q1;                                                              \
+          upk2(x2, p0, p1);                                                                  \
+          p0 = fast_exp2(p0);                                                                \
+          p1 = fast_exp2(p1);                                                                \
+          if (((i >> 1) & 7) < POLY_SHARE) {                                                 \
+            poly_exp2_pair(y2, q0, q1);                                                      \
+          } else {                                                                           \
+            upk2(y2, q0, q1);                                                                \
+            q0 = fast_exp2(q0);                                                              \
+            q1 = fast_exp2(q1);                                                              \
+          }                                                                                  \
+          l_a += p0 + p1;                                                                    \
+          l_b += q0 + q1;                                                                    \
+          packed[i >> 1] = pack_bf16(p0, p1);                                                \
+          packed[16 + (i >> 1)] = pack_bf16(q0, q1);                                         \
+        }                                                                                    \
+        tc_st32(s_addr + (C) * 32, packed);                                                  \
+      }
       if (diagonal) {
         SOFTMAX_HALF(0, true)
         SOFTMAX_HALF(1, true)
       } else {
-        SOFTMAX_HALF(0, false)
-        SOFTMAX_HALF(1, false)
+        const unsigned long long c2 = pk2(SCALE_LOG2, SCALE_LOG2), nm2 = pk2(-m_run, -m_run);
+        SOFTMAX_HALF_FAST(0)
+        SOFTMAX_HALF_FAST(1)
       }
       const float l_blk = l_a + l_b;
       l_run += l_blk;
@@ -341,7 +402,7 @@ extern "C" __global__ void __launch_bounds__(320, 1)
 
 }  // namespace
 
-void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, const ScheduleOverrides&) {
+void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, const ScheduleOverrides& ov) {
   if (a.head_dim != 128 || a.q_len % 256 != 0 || a.k_len % 128 != 0)
     throw PlanError("attention shape not covered by the fused kernel");
   std::string src = std::string(kConvertPrelude) + kTcPreludeShared + kAttentionTemplate;
@@ -354,6 +415,10 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
   replaceAll(src, "@BATCH@", std::to_string(a.batch));
   replaceAll(src, "@CAUSAL@", a.causal ? "1" : "0");
   replaceAll(src, "@SCALE_LOG2@", scale.str());
+  // share of exponentials moved to the FMA pipe: 0/8, 2/8, 4/8 or 8/8 of the pairs of one half,
+  // i.e. none, 1/8, 1/4 or 1/2 of all elements
+  const int poly_share = ov.attention_poly == 1 ? 0 : ov.attention_poly == 2 ? 2 : ov.attention_poly == 4 ? 8 : 4;
+  replaceAll(src, "@POLY_SHARE@", std::to_string(poly_share));
   KernelSource ks;
   ks.name = name;
   ks.family = "attention";

@@ -134,6 +134,7 @@ struct accy_b200_session {
     ov.column_splits = options.column_splits;
     ov.force_simt_gemm = options.force_simt_gemm;
     ov.row_min_blocks = options.row_min_blocks;
+    ov.attention_poly = options.attention_poly;
     ov.sm_count = sm_count;
     x.plan = planProgram(x.program, ov);
     observe("plan", t0);

@@ -266,6 +266,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tpr", type=int, default=0, help="schedule override: threads per row (experiments)")
     ap.add_argument("--vpt", type=int, default=0, help="schedule override: vectors per thread (experiments)")
+    ap.add_argument("--attn-poly", type=int, default=0, help="attention_poly override (experiments)")
     ap.add_argument("--min-blocks", type=int, default=0, help="schedule override: resident CTAs per SM (experiments)")
     args = ap.parse_args()
     name = args.workload
@@ -307,7 +308,7 @@ def main():
         program = cfg.program()
     inputs = cfg.make_inputs()
     session = tensor.Session(device=local, threads_per_row=args.tpr, vectors_per_thread=args.vpt,
-                             row_min_blocks=args.min_blocks)
+                             row_min_blocks=args.min_blocks, attention_poly=args.attn_poly)
     compiled = session.compile(program)
     work = compiled.work()
     d_in = [torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).cuda() for a in inputs]

@@ -478,6 +478,20 @@ class Planner {
       map[i] = static_cast<int>(i);
     }
     int root_node = buildNode(b, v, map);
+    // Sibling outputs with the root's own dims (e.g. a value and its slope, both sums over the
+    // same axis) join this region, so inputs they share are read once (the reference's concat
+    // reduction, reduction.zig:346-420, serves the same purpose).
+    for (auto it = out_slot_of.rbegin(); it != out_slot_of.rend(); ++it) {
+      const uint32_t u = it->first;
+      if (u == v || produced.count(u) || slot_of[u] >= 0 || b.closure.count(u)) continue;
+      const Operation& uop = P.ops[u];
+      if (!(isElementwise(uop.kind) || uop.kind == Kind::reduce)) continue;
+      if (!sameDims(uop.result.dims, ty.dims) || b.nodes.size() > 4000) continue;
+      int node = buildNode(b, u, map);
+      bool listed = false;
+      for (auto& cand : b.coproduce) listed = listed || cand.first == u;
+      if (!listed) b.coproduce.push_back({u, node});
+    }
     // Without any reduction the trailing dims form the column space: enough of them to give a
     // row at least 1024 elements, so flat elementwise programs still fill the machine.
     if (!b.cols_fixed) {

@@ -1,0 +1,113 @@
+"""Programs beyond the five benchmark configurations: other reductions, multi-output programs,
+plain elementwise programs, masks, transposed and reshaped operands, integer and f64 values.
+Each is compiled on CPU (plan + NVRTC) and, on a GPU, run through the C ABI and compared with the
+oracle.  f32 tolerance 1e-5 relative (floor: 1e-6 of the largest magnitude, 1e-3 where values cancel)."""
+import numpy as np
+import pytest
+
+from accy_b200 import tensor
+from oracle import oracle
+
+T = tensor
+
+
+def value_and_slope(b, a):
+    """mismatch and its derivative w.r.t. frequency: two reductions over one fused region"""
+    frequency, time, sample = a
+    phase = frequency.mul(time)
+    gap = phase.sin().sub(sample)
+    value = gap.mul(gap).sum("point")
+    slope = gap.mul(phase.cos()).mul(time).mul(b.scalar("f32", 2.0)).sum("point")
+    return [value, slope]
+
+
+def masked_fill(b, a):
+    x = a[0]
+    dims = x.ty.dims
+    keep = b.iota("i32", dims, "r").compare("ge", b.iota("i32", dims, "c"))
+    return keep.select(x, b.scalar("f32", -1.0))
+
+
+CASES = {
+    "sum_to_scalar": ([T.spec("f32", n=100003)], lambda b, a: a[0].sum("n")),
+    "sum_over_leading_axis": ([T.spec("f32", a=300, b=200)], lambda b, a: a[0].sum("a")),
+    "max_over_two_axes": ([T.spec("f32", a=7, b=33, c=65)], lambda b, a: a[0].max(["b", "c"])),
+    "min_of_interior_axis": ([T.spec("f32", a=5, b=40, c=24)], lambda b, a: a[0].min("b")),
+    "value_and_slope": ([T.spec("f32", guess=24), T.spec("f32", point=4096), T.spec("f32", point=4096)], value_and_slope),
+    "outer_elementwise": ([T.spec("f32", n=257), T.spec("f32", m=129), T.spec("f32", n=257, m=129)],
+                          lambda b, a: a[0].mul(a[1]).add(a[2]).tanh()),
+    "flat_elementwise": ([T.spec("f32", n=1 << 20)], lambda b, a: a[0].mul(a[0]).add(b.scalar("f32", 1.0)).sqrt().log()),
+    "lower_triangle_mask": ([T.spec("f32", r=96, c=96)], masked_fill),
+    "transposed_operand": ([T.spec("f32", a=64, b=48), T.spec("f32", b=48, a=64)], lambda b, a: a[0].add(a[1])),
+    "merge_then_reduce": ([T.spec("f32", a=6, b=10, c=50)], lambda b, a: a[0].merge(["b", "c"], "bc").exp().sum("bc")),
+    "split_axis": ([T.spec("f32", n=600)], lambda b, a: a[0].split("n", p=20, q=30).sum("q")),
+    "int_arithmetic": ([T.spec("i32", n=1000), T.spec("i32", n=1000)], lambda b, a: a[0].mul(a[1]).sub(a[0]).max(a[1])),
+    "double_precision": ([T.spec("f64", r=40, c=300)], lambda b, a: a[0].sub(a[0].mean("c")).abs().sum("c")),
+    "bf16_rowsum": ([T.spec("bf16", r=128, c=512)], lambda b, a: a[0].mul(a[0]).sum("c")),
+    "scalar_program": ([T.spec("f32"), T.spec("f32")], lambda b, a: a[0].div(a[1]).cos()),
+    "passthrough_and_duplicate": ([T.spec("f32", n=100)], lambda b, a: [a[0], a[0].neg(), a[0]]),
+    "two_stage_reduce": ([T.spec("f32", a=50, b=70)], lambda b, a: a[0].sum("b").max("a")),
+    "softmax_then_colsum": ([T.spec("f32", r=64, c=128)],
+                            lambda b, a: a[0].sub(a[0].max("c")).exp().div(a[0].sub(a[0].max("c")).exp().sum("c")).sum("r")),
+}
+
+
+def make_inputs(specs, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for s in specs:
+        shape = tuple(e for _, e in s.dims)
+        if s.dtype == "f32":
+            out.append(rng.uniform(-2.0, 2.0, shape).astype(np.float32))
+        elif s.dtype == "f64":
+            out.append(rng.uniform(-2.0, 2.0, shape))
+        elif s.dtype == "i32":
+            out.append(rng.integers(-1000, 1000, shape, dtype=np.int32))
+        elif s.dtype == "bf16":
+            w = rng.uniform(-2.0, 2.0, shape).astype(np.float32).view(np.uint32)
+            out.append((w >> 16).astype(np.uint16))
+    return out
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_compiles_for_sm100a(cpu_session, name):
+    specs, body = CASES[name]
+    program = tensor.define(name, specs, body)
+    compiled = cpu_session.compile(program)
+    assert compiled.work()["launches"] >= 1
+    assert oracle.describe(program.wire)
+    cpu_session.release(compiled)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_matches_oracle(gpu_session, name):
+    specs, body = CASES[name]
+    program = tensor.define(name, specs, body)
+    inputs = make_inputs(specs, seed=len(name))
+    if name == "scalar_program":
+        inputs = [np.array(1.5, np.float32), np.array(0.7, np.float32)]
+    compiled = gpu_session.compile(program)
+    outs = [np.empty(d.byte_size, np.uint8) for d in compiled.output_descriptors()]
+    gpu_session.invoke(compiled, inputs, outs)
+    gpu_session.release(compiled)
+    mode = "wide" if any(s.dtype == "bf16" for s in specs) else "ref"
+    expected = oracle.run(program.wire, inputs, mode=mode)
+    exact = oracle.run(program.wire, inputs, mode="f64")
+    for got_raw, want, ex, ty in zip(outs, expected, exact, program.output_types):
+        if ty.dtype == "i32":
+            assert np.array_equal(got_raw.view(np.int32), want.reshape(-1))
+            continue
+        if ty.dtype == "bf16":
+            got = (got_raw.view(np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+            want64 = (want.reshape(-1).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+            assert np.max(np.abs(got - want64) / (np.abs(want64) + np.sqrt(np.mean(want64 ** 2)))) < 2e-2
+            continue
+        got = got_raw.view(np.float64 if ty.dtype == "f64" else np.float32).astype(np.float64)
+        want64 = want.reshape(-1).astype(np.float64)
+        ex64 = np.asarray(ex, np.float64).reshape(-1)
+        floor = max(np.abs(ex64).max() * (1e-3 if name in ("value_and_slope", "softmax_then_colsum") else 1e-6), 1e-30)
+        err_gpu = np.max(np.abs(got - ex64) / np.maximum(np.abs(ex64), floor))
+        err_ref = np.max(np.abs(want64 - ex64) / np.maximum(np.abs(ex64), floor))
+        tol = 1e-12 if ty.dtype == "f64" else 1e-5
+        assert err_gpu < tol + err_ref, (name, err_gpu, err_ref)

@@ -109,6 +109,18 @@ WORKLOADS = {
 }
 
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) taken from the ncu captures
+# summarised under profiles/, scaled to the default size where the traffic grows with the units
+# processed: bytes per row (softmax_layernorm: 26 988 B per 4096-column row; the writes of the last
+# ~100 MB are still in L2 when the kernel ends, so this is below the 32 768 B the row moves) and
+# bytes per launch (mismatch: the two point vectors, the guesses and the result).  The tensor-core
+# kernels re-read operands through L2 in a size-dependent way, so no scaled figure is given.
+NCU_TRAFFIC = {
+    "softmax_layernorm": lambda cfg: 26988.0 * dict(cfg.specs[0].dims)["row"],
+    "mismatch": lambda cfg: 4.0 * (2 * dict(cfg.specs[1].dims)["point"] + 2 * dict(cfg.specs[0].dims)["guess"]) * 0.957,
+}
+
+
 def _size_args(name, cfg):
     """(label, extent) pairs that rebuild a config of the same size with another seed"""
     dims = {n: e for s in cfg.specs for n, e in s.dims}
@@ -407,7 +419,9 @@ def main():
             achieved = cfg.work["flops"] / 1e12 / (avg_ms / 1e3)
             peak, peak_unit = peaks["bf16_tflops"], "TFLOP/s"
         roofline = {"bound": bound, "achieved": achieved, "peak": peak, "unit": peak_unit, "frac": achieved / peak,
-                    "traffic": None, "peak_source": peaks["source"], "kernel_ms": avg_ms,
+                    "traffic": NCU_TRAFFIC[name](cfg) if name in NCU_TRAFFIC else None,
+                    "peak_source": peaks["source"], "peak_sustained": peaks["bf16_tflops_sustained"] if bound == "tensor" else None,
+                    "kernel_ms": avg_ms,
                     "launches_per_step": work["launches"]}
         cpu = None
         if world == 1 and not args.no_cpu_baseline:

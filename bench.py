@@ -242,7 +242,9 @@ def reference_arm(args, name, cfg):
     if rank != 0:
         return
     from oracle import oracle
-    threads = oracle.lib().oracle_max_threads()
+    # every host core this process may use (torchrun sets OMP_NUM_THREADS=1, so the OpenMP default is not it)
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    oracle.lib()
     inputs = cfg.make_inputs()
     metric, unit, _ = WORKLOADS[name]
     for _ in range(max(1, min(args.warmup, 1))):
@@ -352,6 +354,7 @@ def main():
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     torch.cuda.synchronize()
+    load_t0 = time.perf_counter()   # clock samples count from here: the GPU is under load until load_t1
     wall0 = time.perf_counter()
     for i in range(args.steps):
         if flush is not None:

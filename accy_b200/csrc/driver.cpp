@@ -154,11 +154,15 @@ struct Nvrtc {
 } g_nvrtc;
 
 void loadNvrtc() {
-  const char* names[] = {"libnvrtc.so.12", "/usr/local/cuda/lib64/libnvrtc.so.12", "libnvrtc.so",
-                         "/usr/local/cuda/lib64/libnvrtc.so"};
+  // The toolkit's own library comes first: a process that imported another CUDA package may already
+  // hold an older libnvrtc.so.12 under the bare name, and the kernels use the newest PTX the toolkit
+  // the library was built against accepts.  ACCY_B200_NVRTC names a specific file.
+  const char* names[] = {getenv("ACCY_B200_NVRTC"), "/usr/local/cuda/lib64/libnvrtc.so.12", "libnvrtc.so.12",
+                         "/usr/local/cuda/lib64/libnvrtc.so", "libnvrtc.so"};
   void* lib = nullptr;
   for (const char* n : names) {
-    lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (!n || !*n) continue;
+    lib = dlopen(n, RTLD_NOW | RTLD_LOCAL);
     if (lib) break;
   }
   if (!lib) throw std::runtime_error("cannot load libnvrtc.so.12 (needed to build sm_100a kernels)");

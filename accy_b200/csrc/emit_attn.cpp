@@ -50,6 +50,10 @@ const char* kAttentionTemplate = R"CUDA(
 #define SCALE_LOG2 @SCALE_LOG2@f
 #define RESCALE_THRESHOLD 8.0f
 #define POLY_SHARE @POLY_SHARE@   // of every 8 pairs in the second half of a 64-column group
+#define HALF_HANDOFF @HALF_HANDOFF@   // P is handed to the MMA issuer 64 keys at a time
+#define ABLATE @ABLATE@
+#define BH_MAJOR @BH_MAJOR@
+#define ATTN_TRACE @TRACE@        // development aid: one CTA records clock stamps of its hand-offs and prints them
 #ifndef INFINITY
 #define INFINITY __int_as_float(0x7f800000)
 #endif
@@ -82,6 +86,13 @@ __device__ __forceinline__ void poly_exp2_pair(unsigned long long x2, float& out
   out1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
+// three-input max (one instruction on sm_100) where the compiler's PTX version has it
+#if __CUDACC_VER_MAJOR__ > 12 || (__CUDACC_VER_MAJOR__ == 12 && __CUDACC_VER_MINOR__ >= 9)
+__device__ __forceinline__ float max3(float a, float b, float c) { float r; asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c)); return r; }
+#else
+__device__ __forceinline__ float max3(float a, float b, float c) { return fmaxf(a, fmaxf(b, c)); }
+#endif
+
 __device__ __forceinline__ void tc_st32(unsigned int taddr, const unsigned int* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -104,16 +115,33 @@ extern "C" __global__ void __launch_bounds__(320, 1)
   unsigned char* v_smem = k_smem + KV_STAGES * TILE_BYTES;
   unsigned long long* bars = (unsigned long long*)(v_smem + KV_STAGES * TILE_BYTES);
   // bars: 0 q_full | 1..2 k_full | 3..4 k_empty | 5..6 v_full | 7..8 v_empty | 9..10 s_full | 11..12 p_full | 13..14 pv_done
-  unsigned int* tmem_holder = (unsigned int*)(bars + 16);
+  //       15..16 p_half (the first 64 keys of P are in TMEM)
+  unsigned int* tmem_holder = (unsigned int*)(bars + 24);
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
   const unsigned int bar0 = smem_u32(bars);
 #define BAR(i) (bar0 + 8u * (i))
+#if ATTN_TRACE
+  unsigned int* trace = (unsigned int*)(bars + 32);
+#define TRACE_SOFTMAX @TRACE_SM@
+#define TRACE_J0 8
+#define TRACE_N 6
+#define TR(role, j, e) if (blockIdx.x == 0 && (j) >= TRACE_J0 && (j) < TRACE_J0 + TRACE_N) trace[((role) * TRACE_N + (j) - TRACE_J0) * 8 + (e)] = (unsigned int)clock64();
+#else
+#define TRACE_SOFTMAX 0
+#define TR(role, j, e)
+#endif
   const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // work item: heaviest query pairs first
   const int n_pairs = SEQ_Q / (2 * TILE);
+#if BH_MAJOR
+  // the CTAs of one (batch, head) are launched together so that its K and V stay in L2
+  const int pair = n_pairs - 1 - (int)(blockIdx.x % n_pairs);
+  const int bh = (int)(blockIdx.x / n_pairs);
+#else
   const int pair = n_pairs - 1 - (int)(blockIdx.x / BATCH);
   const int bh = (int)(blockIdx.x % BATCH);
+#endif
   const int q_row0 = pair * 2 * TILE;
   // key blocks each tile attends to
 #if CAUSAL
@@ -126,6 +154,7 @@ extern "C" __global__ void __launch_bounds__(320, 1)
     for (int i = 0; i < 11; ++i) mbar_init(BAR(i), 1);
     mbar_init(BAR(11), 4); mbar_init(BAR(12), 4);
     mbar_init(BAR(13), 1); mbar_init(BAR(14), 1);
+    mbar_init(BAR(15), 4); mbar_init(BAR(16), 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -151,13 +180,17 @@ extern "C" __global__ void __launch_bounds__(320, 1)
         const int stage = j % KV_STAGES;
         const unsigned int ph = (unsigned int)((j / KV_STAGES) & 1);
         if (!mbar_wait(BAR(3 + stage), ph ^ 1u, abort_flag)) { ok = false; break; }
+        if (ABLATE == 5 && j >= 2) mbar_arrive(BAR(1 + stage)); else {
         mbar_expect_tx(BAR(1 + stage), TILE_BYTES);
         for (int h = 0; h < 2; ++h)
           tma_load_3d(smem_u32(k_smem + stage * TILE_BYTES + h * HALF_BYTES), &map_k, BAR(1 + stage), h * 64, j * TILE, bh);
+        }
         if (!mbar_wait(BAR(7 + stage), ph ^ 1u, abort_flag)) { ok = false; break; }
+        if (ABLATE == 5 && j >= 2) mbar_arrive(BAR(5 + stage)); else {
         mbar_expect_tx(BAR(5 + stage), TILE_BYTES);
         for (int h = 0; h < 2; ++h)
           tma_load_3d(smem_u32(v_smem + stage * TILE_BYTES + h * HALF_BYTES), &map_v, BAR(5 + stage), h * 64, j * TILE, bh);
+        }
       }
     }
   } else if (warp == 1) {
@@ -167,6 +200,9 @@ extern "C" __global__ void __launch_bounds__(320, 1)
       const unsigned int idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned int)(TILE >> 3) << 17) | ((unsigned int)(TILE >> 4) << 24);
       const unsigned int idesc_o = idesc_s | (1u << 16);
       bool ok = true;
+      auto wait_kv = [&](int base, int j) {
+        return mbar_wait(BAR(base + j % KV_STAGES), (unsigned int)((j / KV_STAGES) & 1), abort_flag);
+      };
       auto issue_s = [&](int t, int j) {
         const int stage = j % KV_STAGES;
         const unsigned int qa = smem_u32(q_smem + t * TILE_BYTES), ka = smem_u32(k_smem + stage * TILE_BYTES);
@@ -175,19 +211,52 @@ extern "C" __global__ void __launch_bounds__(320, 1)
           const unsigned int off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
           tc_mma_ss(tmem_base + t * TILE, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
         }
+        if (t == 0) { TR(3, j - 1, 7) }
         tc_commit(BAR(9 + t));
       };
-      auto issue_pv = [&](int t, int j) {
+      auto issue_pv_part = [&](int t, int j, int k0) {
         const int stage = j % KV_STAGES;
         const unsigned int va = smem_u32(v_smem + stage * TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < TILE / 16; ++k)
+        for (int k = k0; k < k0 + TILE / 32; ++k)
           tc_mma_ts(tmem_base + 2 * TILE + t * TILE, tmem_base + t * TILE + k * 8,
                     smem_desc(va + k * 16 * 128, HALF_BYTES, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-        tc_commit(BAR(13 + t));
       };
-      auto wait_kv = [&](int base, int j) {
-        return mbar_wait(BAR(base + j % KV_STAGES), (unsigned int)((j / KV_STAGES) & 1), abort_flag);
+      // O_t += P_t V once P_t is in TMEM (in two halves of 64 keys when the softmax hands them over so)
+      auto issue_pv = [&](int t, int j, bool need_v) {
+        const unsigned int ph = (unsigned int)(j & 1);
+        if (HALF_HANDOFF) {
+          if (!(mbar_wait(BAR(15 + t), ph, abort_flag) && (!need_v || wait_kv(5, j)))) return false;
+          TR(0, j, t * 4 + 0)
+          tc_fence_after();
+          issue_pv_part(t, j, 0);
+          if (!mbar_wait(BAR(11 + t), ph, abort_flag)) return false;
+          TR(0, j, t * 4 + 1)
+          tc_fence_after();
+          issue_pv_part(t, j, TILE / 32);
+        } else {
+          if (t == 0) { TR(3, j, 0) }
+          if (!mbar_wait(BAR(11 + t), ph, abort_flag)) return false;
+          if (t == 0) { TR(3, j, 1) }
+          if (need_v && !wait_kv(5, j)) return false;
+          if (t == 0) { TR(3, j, 2) }
+          TR(0, j, t * 4 + 1)
+#if ATTN_TRACE
+          if (t == 0 && blockIdx.x == 0 && j >= TRACE_J0 && j < TRACE_J0 + TRACE_N) {
+            unsigned long long ns; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+            trace[((0) * TRACE_N + j - TRACE_J0) * 8 + 0] = (unsigned int)ns;
+          }
+#endif
+          tc_fence_after();
+          issue_pv_part(t, j, 0);
+          if (t == 0) { TR(3, j, 3) }
+          issue_pv_part(t, j, TILE / 32);
+          if (t == 0) { TR(3, j, 4) }
+        }
+        tc_commit(BAR(13 + t));
+        if (t == 0) { TR(3, j, 5) }
+        TR(0, j, t * 4 + 2)
+        return true;
       };
       ok = mbar_wait(BAR(0), 0, abort_flag) && wait_kv(1, 0);
       if (ok) {
@@ -197,28 +266,26 @@ extern "C" __global__ void __launch_bounds__(320, 1)
         tc_commit(BAR(3));   // K stage 0 is free once both S MMAs have read it
       }
       for (int j = 0; ok && j < n1; ++j) {
-        const unsigned int ph = (unsigned int)(j & 1);
         bool k_next = false;
         if (j < n0) {
-          if (!(mbar_wait(BAR(11), ph, abort_flag) && wait_kv(5, j))) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(0, j);
+          if (!issue_pv(0, j, true)) { ok = false; break; }
           if (j + 1 < n0) {
             if (!wait_kv(1, j + 1)) { ok = false; break; }
             k_next = true;
             tc_fence_after();
+            TR(3, j, 6)
             issue_s(0, j + 1);
+            TR(0, j, 3)
           }
         }
-        if (!(mbar_wait(BAR(12), ph, abort_flag) && wait_kv(5, j))) { ok = false; break; }
-        tc_fence_after();
-        issue_pv(1, j);
+        if (!issue_pv(1, j, j >= n0)) { ok = false; break; }   // V(j) was awaited for tile 0 already
         tc_commit(BAR(7 + j % KV_STAGES));   // V stage free
         if (j + 1 < n1) {
           if (!k_next && !wait_kv(1, j + 1)) { ok = false; break; }
           tc_fence_after();
           issue_s(1, j + 1);
           tc_commit(BAR(3 + (j + 1) % KV_STAGES));   // K stage free
+          TR(0, j, 7)
         }
       }
     }
@@ -234,19 +301,29 @@ extern "C" __global__ void __launch_bounds__(320, 1)
     float m_run = -INFINITY, l_run = 0.0f;
     bool ok = true;
     for (int j = 0; ok && j < n_t; ++j) {
+      if (((TRACE_SOFTMAX >> 0) & 1) && row == 0) { TR(1 + t, j, 0) }
       if (!mbar_wait(BAR(9 + t), (unsigned int)(j & 1), abort_flag)) { ok = false; break; }
+      if (((TRACE_SOFTMAX >> 1) & 1) && row == 0) { TR(1 + t, j, 1) }
       tc_fence_after();
       const bool diagonal = CAUSAL && (j == n_t - 1);
-      // pass 1: row max.  The scale is positive, so the max is taken over the raw scores and
-      // scaled once; the four loads are in flight together and four chains fold them.
+      // the whole score row (128 columns) is read once and stays in registers for the row max
+      // and for the exponentials; the four loads are in flight together
+      unsigned int r0[32], r1[32], r2[32], r3[32];
+      if (ABLATE == 4) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { r0[i] = (unsigned int)(j * 77 + i + row) << 18; r1[i] = r0[i] + 3; r2[i] = r0[i] + 2; r3[i] = r0[i] + 1; }
+      } else {
+      tc_ld32(s_addr, r0);
+      tc_ld32(s_addr + 32, r1);
+      tc_ld32(s_addr + 64, r2);
+      tc_ld32(s_addr + 96, r3);
+      tc_wait_ld();
+      }
+      if (((TRACE_SOFTMAX >> 2) & 1) && row == 0) { TR(1 + t, j, 2) }
+      // row max.  The scale is positive, so the max is taken over the raw scores and scaled once;
+      // four chains of three-input max fold the 128 values.
       float m_blk;
       {
-        unsigned int r0[32], r1[32], r2[32], r3[32];
-        tc_ld32(s_addr, r0);
-        tc_ld32(s_addr + 32, r1);
-        tc_ld32(s_addr + 64, r2);
-        tc_ld32(s_addr + 96, r3);
-        tc_wait_ld();
         float a = -INFINITY, b = -INFINITY, c = -INFINITY, d = -INFINITY;
         if (diagonal) {
 #pragma unroll
@@ -256,13 +333,15 @@ extern "C" __global__ void __launch_bounds__(320, 1)
             c = fmaxf(c, 64 + i > row ? -INFINITY : __uint_as_float(r2[i]));
             d = fmaxf(d, 96 + i > row ? -INFINITY : __uint_as_float(r3[i]));
           }
+        } else if (ABLATE == 2) {
+          a = b = c = d = 1.0f;
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            a = fmaxf(a, __uint_as_float(r0[i]));
-            b = fmaxf(b, __uint_as_float(r1[i]));
-            c = fmaxf(c, __uint_as_float(r2[i]));
-            d = fmaxf(d, __uint_as_float(r3[i]));
+          for (int i = 0; i < 32; i += 2) {
+            a = max3(a, __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
+            b = max3(b, __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
+            c = max3(c, __uint_as_float(r2[i]), __uint_as_float(r2[i + 1]));
+            d = max3(d, __uint_as_float(r3[i]), __uint_as_float(r3[i + 1]));
           }
         }
         m_blk = fmaxf(fmaxf(a, b), fmaxf(c, d)) * SCALE_LOG2;
@@ -278,93 +357,93 @@ extern "C" __global__ void __launch_bounds__(320, 1)
           // O of this tile is up to date once the previous P V product has completed
           if (!mbar_wait(BAR(13 + t), (unsigned int)((j - 1) & 1), abort_flag)) { ok = false; break; }
           tc_fence_after();
+          // rare path: the first score registers serve as scratch and the scores are read again
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
-            unsigned int r[32];
-            tc_ld32(o_addr + c * 32, r);
+            tc_ld32(o_addr + c * 32, r0);
             tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
-            tc_st32(o_addr + c * 32, r);
+            for (int i = 0; i < 32; ++i) r0[i] = __float_as_uint(__uint_as_float(r0[i]) * factor);
+            tc_st32(o_addr + c * 32, r0);
           }
           tc_wait_st();
+          tc_ld32(s_addr, r0);
+          tc_ld32(s_addr + 32, r1);
+          tc_ld32(s_addr + 64, r2);
+          tc_ld32(s_addr + 96, r3);
+          tc_wait_ld();
         }
       }
-      // pass 2: p = 2^(x - m), row sum, bf16 pairs written over S (64 columns at a time: the
-      // columns a thread overwrites are columns it has already read)
-      float l_a = 0.0f, l_b = 0.0f;
-#define SOFTMAX_HALF(C, MASKED)                                                              \
-      {                                                                                      \
-        unsigned int ra[32], rb[32], packed[32];                                             \
-        tc_ld32(s_addr + (C) * 64, ra);                                                      \
-        tc_ld32(s_addr + (C) * 64 + 32, rb);                                                 \
-        tc_wait_ld();                                                                        \
-        _Pragma("unroll")                                                                    \
-        for (int i = 0; i < 32; i += 2) {                                                    \
-          float x0 = fmaf(__uint_as_float(ra[i]), SCALE_LOG2, -m_run);                       \
-          float x1 = fmaf(__uint_as_float(ra[i + 1]), SCALE_LOG2, -m_run);                   \
-          float y0 = fmaf(__uint_as_float(rb[i]), SCALE_LOG2, -m_run);                       \
-          float y1 = fmaf(__uint_as_float(rb[i + 1]), SCALE_LOG2, -m_run);                   \
-          if (MASKED) {                                                                      \
-            const int col = (C) * 64 + i;                                                    \
-            if (col > row) x0 = -INFINITY;                                                   \
-            if (col + 1 > row) x1 = -INFINITY;                                               \
-            if (col + 32 > row) y0 = -INFINITY;                                              \
-            if (col + 33 > row) y1 = -INFINITY;                                              \
-          }                                                                                  \
-          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), q0 = fast_exp2(y0), q1 = fast_exp2(y1); \
-          l_a += p0 + p1;                                                                    \
-          l_b += q0 + q1;                                                                    \
-          packed[i >> 1] = pack_bf16(p0, p1);                                                \
-          packed[16 + (i >> 1)] = pack_bf16(q0, q1);                                         \
-        }                                                                                    \
-        tc_st32(s_addr + (C) * 32, packed);                                                  \
-      }
-      // unmasked blocks: the scale-and-shift is a packed FMA, and a fixed share of the
-      // exponentials (POLY_SHARE of every 8 pairs) runs on the FMA pipe to relieve the
-      // special-function unit, which otherwise limits the kernel as much as the tensor cores do
-#define SOFTMAX_HALF_FAST(C)                                                                 \
-      {                                                                                      \
-        unsigned int ra[32], rb[32], packed[32];                                             \
-        tc_ld32(s_addr + (C) * 64, ra);                                                      \
-        tc_ld32(s_addr + (C) * 64 + 32, rb);                                                 \
-        tc_wait_ld();                                                                        \
-        _Pragma("unroll")                                                                    \
-        for (int i = 0; i < 32; i += 2) {                                                    \
-          const unsigned long long x2 = fma2(pk2u(ra[i], ra[i + 1]), c2, nm2);               \
-          const unsigned long long y2 = fma2(pk2u(rb[i], rb[i + 1]), c2, nm2);               \
-          float p0, p1, q0, q1;                                                              \
+      // p = 2^(scale * s - m) as packed FMAs and ex2, packed row sums, bf16 pairs written over S
+      // 64 keys at a time.  A fixed share of the exponentials (POLY_SHARE of every 8 pairs of the
+      // odd quarters) can run on the FMA pipe instead of the special-function unit.
+      if (((TRACE_SOFTMAX >> 3) & 1) && row == 0) { TR(1 + t, j, 3) }
+      const unsigned long long c2 = pk2(SCALE_LOG2, SCALE_LOG2), nm2 = pk2(-m_run, -m_run);
+      unsigned long long l2a = pk2(0.0f, 0.0f), l2b = l2a;
+#define EXP_QUARTER(R, COL0, OUT, AT, ACC, MASKED, POLY)                                     \
+      _Pragma("unroll")                                                                      \
+      for (int i = 0; i < 32; i += 2) {                                                      \
+        const unsigned long long x2 = fma2(pk2u(R[i], R[i + 1]), c2, nm2);                   \
+        float p0, p1;                                                                        \
+        if (!(MASKED) && (POLY) && ((i >> 1) & 7) < POLY_SHARE) {                            \
+          poly_exp2_pair(x2, p0, p1);                                                        \
+        } else {                                                                             \
           upk2(x2, p0, p1);                                                                  \
+          if (MASKED) {                                                                      \
+            if ((COL0) + i > row) p0 = -INFINITY;                                            \
+            if ((COL0) + i + 1 > row) p1 = -INFINITY;                                        \
+          }                                                                                  \
+          if (ABLATE != 1) {                                                                 \
           p0 = fast_exp2(p0);                                                                \
           p1 = fast_exp2(p1);                                                                \
-          if (((i >> 1) & 7) < POLY_SHARE) {                                                 \
-            poly_exp2_pair(y2, q0, q1);                                                      \
-          } else {                                                                           \
-            upk2(y2, q0, q1);                                                                \
-            q0 = fast_exp2(q0);                                                              \
-            q1 = fast_exp2(q1);                                                              \
           }                                                                                  \
-          l_a += p0 + p1;                                                                    \
-          l_b += q0 + q1;                                                                    \
-          packed[i >> 1] = pack_bf16(p0, p1);                                                \
-          packed[16 + (i >> 1)] = pack_bf16(q0, q1);                                         \
         }                                                                                    \
-        tc_st32(s_addr + (C) * 32, packed);                                                  \
+        ACC = add2(ACC, pk2(p0, p1));                                                        \
+        OUT[(AT) + (i >> 1)] = pack_bf16(p0, p1);                                            \
       }
-      if (diagonal) {
-        SOFTMAX_HALF(0, true)
-        SOFTMAX_HALF(1, true)
-      } else {
-        const unsigned long long c2 = pk2(SCALE_LOG2, SCALE_LOG2), nm2 = pk2(-m_run, -m_run);
-        SOFTMAX_HALF_FAST(0)
-        SOFTMAX_HALF_FAST(1)
+#define HALF_READY()                                                                         \
+      if (HALF_HANDOFF) {                                                                    \
+        tc_wait_st();                                                                        \
+        tc_fence_before();                                                                   \
+        __syncwarp();                                                                        \
+        if (lane == 0) mbar_arrive(BAR(15 + t));                                             \
       }
-      const float l_blk = l_a + l_b;
-      l_run += l_blk;
+      {
+        unsigned int pa[32], pb[32];
+        if (diagonal) {
+          EXP_QUARTER(r0, 0, pa, 0, l2a, true, false)
+          EXP_QUARTER(r1, 32, pa, 16, l2b, true, false)
+          tc_st32(s_addr, pa);
+          EXP_QUARTER(r2, 64, pb, 0, l2a, true, false)
+          HALF_READY()
+          EXP_QUARTER(r3, 96, pb, 16, l2b, true, false)
+          tc_st32(s_addr + 32, pb);
+        } else {
+          EXP_QUARTER(r0, 0, pa, 0, l2a, false, false)
+          EXP_QUARTER(r1, 32, pa, 16, l2b, false, true)
+          if (ABLATE != 3) tc_st32(s_addr, pa); else l2a = add2(l2a, pk2u(pa[0] ^ pa[5] ^ pa[17], pa[31] ^ pa[9]));
+          if (((TRACE_SOFTMAX >> 4) & 1) && row == 0) { TR(1 + t, j, 4) }
+          EXP_QUARTER(r2, 64, pb, 0, l2a, false, false)
+          HALF_READY()
+          if (((TRACE_SOFTMAX >> 5) & 1) && row == 0) { TR(1 + t, j, 5) }
+          EXP_QUARTER(r3, 96, pb, 16, l2b, false, true)
+          if (ABLATE != 3) tc_st32(s_addr + 32, pb); else l2a = add2(l2a, pk2u(pb[0] ^ pb[5] ^ pb[17], pb[31] ^ pb[9]));
+        }
+      }
+      {
+        float s0, s1;
+        upk2(add2(l2a, l2b), s0, s1);
+        l_run += s0 + s1;
+      }
+      if (((TRACE_SOFTMAX >> 6) & 1) && row == 0) { TR(1 + t, j, 6) }
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(BAR(11 + t));
+      if (((TRACE_SOFTMAX >> 7) & 1) && row == 0) { TR(1 + t, j, 7) }
+#if ATTN_TRACE
+      if (!((TRACE_SOFTMAX >> 7) & 1) && lane == 0) { TR(1 + t, j, 4 + (int)quarter) }
+#endif
     }
     // epilogue: O / l -> bf16 -> global
     if (ok && mbar_wait(BAR(13 + t), (unsigned int)((n_t - 1) & 1), abort_flag)) {
@@ -394,6 +473,15 @@ extern "C" __global__ void __launch_bounds__(320, 1)
   }
   tc_fence_before();
   __syncthreads();
+#if ATTN_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (int role = 0; role < 4; ++role)
+      for (int j = 0; j < TRACE_N; ++j) {
+        const unsigned int* e = trace + (role * TRACE_N + j) * 8;
+        printf("TRACE role %d j %d : %u %u %u %u %u %u %u %u\n", role, TRACE_J0 + j, e[0], e[1], e[2], e[3], e[4], e[5], e[6], e[7]);
+      }
+  }
+#endif
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(512) : "memory");
   }
@@ -420,8 +508,15 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
   // measured on the causal 4096 x 128 benchmark: none 847, 1/8 832, 1/4 812, 1/2 797 TFLOP/s, so the
   // automatic choice is none (the kernel is bound by MMA/softmax hand-off latency, not by the
   // special-function unit)
-  const int poly_share = ov.attention_poly == 2 ? 2 : ov.attention_poly == 3 ? 4 : ov.attention_poly == 4 ? 8 : 0;
+  const int poly_code = ov.attention_poly & 7;
+  const int poly_share = poly_code == 2 ? 2 : poly_code == 3 ? 4 : poly_code == 4 ? 8 : 0;
   replaceAll(src, "@POLY_SHARE@", std::to_string(poly_share));
+  replaceAll(src, "@HALF_HANDOFF@", (ov.attention_poly & 8) ? "0" : "1");
+  const bool trace = (ov.attention_poly & 16) != 0;
+  replaceAll(src, "@BH_MAJOR@", (ov.attention_poly & 256) ? "0" : "1");
+  replaceAll(src, "@ABLATE@", std::to_string((ov.attention_poly >> 5) & 7));
+  replaceAll(src, "@TRACE@", trace ? "1" : "0");
+  replaceAll(src, "@TRACE_SM@", std::to_string((ov.attention_poly >> 9) & 255));
   KernelSource ks;
   ks.name = name;
   ks.family = "attention";
@@ -434,7 +529,7 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
   if (items > 0x7fffffffll) throw PlanError("too many attention work items");
   l.grid[0] = static_cast<uint32_t>(items);
   l.block[0] = 320;
-  l.dynamic_smem = 6 * 32768 + 1024 + 256;
+  l.dynamic_smem = 6 * 32768 + 1024 + 256 + (trace ? 4096 : 0);
   l.label = name;
   auto map = [&](int slot, int64_t seq) {
     KernelArg m;

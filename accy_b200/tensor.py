@@ -405,7 +405,8 @@ class Session:
             self._h = None
 
     def __del__(self):
-        self.deinit()
+        if lib is not None:   # module globals are cleared at interpreter shutdown
+            self.deinit()
 
     def _check(self, status):
         if status:

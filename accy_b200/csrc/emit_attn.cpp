@@ -195,39 +195,44 @@ extern "C" __global__ void __launch_bounds__(320, 1)
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    // One thread issues every MMA, tile 0 then tile 1 in turn: that order keeps the two tiles half
+    // a period apart, so one tile's softmax runs (and has the special-function unit to itself)
+    // while the other tile's MMAs execute.  The tensor pipe takes MMAs no faster than this thread
+    // hands them over, so everything else it does (barrier probes, fences, commits) is kept short
+    // and the operand barriers, normally long complete, are probed before the wait for P.
     if (lane == 0) {
       // S = Q K^T: A, B K-major, M = N = 128.  O += P V: A from TMEM, B = V with dim contiguous (N-major).
       const unsigned int idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned int)(TILE >> 3) << 17) | ((unsigned int)(TILE >> 4) << 24);
       const unsigned int idesc_o = idesc_s | (1u << 16);
+      const unsigned long long q_desc0 = smem_desc(smem_u32(q_smem), 16, 1024);
+      const unsigned long long q_desc1 = smem_desc(smem_u32(q_smem + TILE_BYTES), 16, 1024);
       bool ok = true;
       auto wait_kv = [&](int base, int j) {
         return mbar_wait(BAR(base + j % KV_STAGES), (unsigned int)((j / KV_STAGES) & 1), abort_flag);
       };
+      // descriptors advance by adding to their 14-bit address field (16-byte units)
       auto issue_s = [&](int t, int j) {
-        const int stage = j % KV_STAGES;
-        const unsigned int qa = smem_u32(q_smem + t * TILE_BYTES), ka = smem_u32(k_smem + stage * TILE_BYTES);
+        const unsigned long long k_desc = smem_desc(smem_u32(k_smem + (j % KV_STAGES) * TILE_BYTES), 16, 1024);
+        const unsigned long long q_desc = t == 0 ? q_desc0 : q_desc1;
 #pragma unroll
         for (int k = 0; k < HEAD_DIM / 16; ++k) {
-          const unsigned int off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          tc_mma_ss(tmem_base + t * TILE, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+          const unsigned long long off = (unsigned long long)(((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4);
+          tc_mma_ss(tmem_base + t * TILE, q_desc + off, k_desc + off, idesc_s, k > 0 ? 1u : 0u);
         }
-        if (t == 0) { TR(3, j - 1, 7) }
         tc_commit(BAR(9 + t));
       };
       auto issue_pv_part = [&](int t, int j, int k0) {
-        const int stage = j % KV_STAGES;
-        const unsigned int va = smem_u32(v_smem + stage * TILE_BYTES);
+        const unsigned long long v_desc = smem_desc(smem_u32(v_smem + (j % KV_STAGES) * TILE_BYTES), HALF_BYTES, 1024);
 #pragma unroll
         for (int k = k0; k < k0 + TILE / 32; ++k)
           tc_mma_ts(tmem_base + 2 * TILE + t * TILE, tmem_base + t * TILE + k * 8,
-                    smem_desc(va + k * 16 * 128, HALF_BYTES, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    v_desc + (unsigned long long)((k * 16 * 128) >> 4), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
       };
       // O_t += P_t V once P_t is in TMEM (in two halves of 64 keys when the softmax hands them over so)
-      auto issue_pv = [&](int t, int j, bool need_v) {
+      auto issue_pv = [&](int t, int j) {
         const unsigned int ph = (unsigned int)(j & 1);
         if (HALF_HANDOFF) {
-          if (!(mbar_wait(BAR(15 + t), ph, abort_flag) && (!need_v || wait_kv(5, j)))) return false;
-          TR(0, j, t * 4 + 0)
+          if (!mbar_wait(BAR(15 + t), ph, abort_flag)) return false;
           tc_fence_after();
           issue_pv_part(t, j, 0);
           if (!mbar_wait(BAR(11 + t), ph, abort_flag)) return false;
@@ -235,26 +240,13 @@ extern "C" __global__ void __launch_bounds__(320, 1)
           tc_fence_after();
           issue_pv_part(t, j, TILE / 32);
         } else {
-          if (t == 0) { TR(3, j, 0) }
           if (!mbar_wait(BAR(11 + t), ph, abort_flag)) return false;
-          if (t == 0) { TR(3, j, 1) }
-          if (need_v && !wait_kv(5, j)) return false;
-          if (t == 0) { TR(3, j, 2) }
           TR(0, j, t * 4 + 1)
-#if ATTN_TRACE
-          if (t == 0 && blockIdx.x == 0 && j >= TRACE_J0 && j < TRACE_J0 + TRACE_N) {
-            unsigned long long ns; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
-            trace[((0) * TRACE_N + j - TRACE_J0) * 8 + 0] = (unsigned int)ns;
-          }
-#endif
           tc_fence_after();
           issue_pv_part(t, j, 0);
-          if (t == 0) { TR(3, j, 3) }
           issue_pv_part(t, j, TILE / 32);
-          if (t == 0) { TR(3, j, 4) }
         }
         tc_commit(BAR(13 + t));
-        if (t == 0) { TR(3, j, 5) }
         TR(0, j, t * 4 + 2)
         return true;
       };
@@ -266,30 +258,32 @@ extern "C" __global__ void __launch_bounds__(320, 1)
         tc_commit(BAR(3));   // K stage 0 is free once both S MMAs have read it
       }
       for (int j = 0; ok && j < n1; ++j) {
-        bool k_next = false;
+        TR(0, j, 0)
+        // operands of this step: V(j) and K(j + 1)
+        if (!wait_kv(5, j) || (j + 1 < n1 && !wait_kv(1, j + 1))) { ok = false; break; }
         if (j < n0) {
-          if (!issue_pv(0, j, true)) { ok = false; break; }
+          if (!issue_pv(0, j)) { ok = false; break; }
           if (j + 1 < n0) {
-            if (!wait_kv(1, j + 1)) { ok = false; break; }
-            k_next = true;
-            tc_fence_after();
-            TR(3, j, 6)
             issue_s(0, j + 1);
             TR(0, j, 3)
           }
         }
-        if (!issue_pv(1, j, j >= n0)) { ok = false; break; }   // V(j) was awaited for tile 0 already
+        if (!issue_pv(1, j)) { ok = false; break; }
         tc_commit(BAR(7 + j % KV_STAGES));   // V stage free
         if (j + 1 < n1) {
-          if (!k_next && !wait_kv(1, j + 1)) { ok = false; break; }
-          tc_fence_after();
           issue_s(1, j + 1);
           tc_commit(BAR(3 + (j + 1) % KV_STAGES));   // K stage free
           TR(0, j, 7)
         }
+#if ATTN_TRACE
+        if (blockIdx.x == 0 && j >= TRACE_J0 && j < TRACE_J0 + TRACE_N) {
+          unsigned long long ns; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+          trace[(3 * TRACE_N + j - TRACE_J0) * 8 + 0] = (unsigned int)ns;
+        }
+#endif
       }
     }
-  } else {
+  } else if (warp >= 2 && warp < 10) {
     // ---------------- softmax + correction + epilogue: warps 2..5 tile 0, warps 6..9 tile 1 ----------------
     const int t = (warp - 2) >> 2;
     const unsigned int quarter = warp & 3u;

@@ -104,7 +104,7 @@ __device__ __forceinline__ void tc_st32(unsigned int taddr, const unsigned int* 
                : "memory");
 }
 
-extern "C" __global__ void __launch_bounds__(320, 1)
+extern "C" __global__ void __launch_bounds__(384, 1)
 @KERNEL@(const __grid_constant__ TensorMap map_q, const __grid_constant__ TensorMap map_k,
          const __grid_constant__ TensorMap map_v, unsigned short* __restrict__ O, int* __restrict__ status) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -118,6 +118,8 @@ extern "C" __global__ void __launch_bounds__(320, 1)
   //       15..16 p_half (the first 64 keys of P are in TMEM)
   unsigned int* tmem_holder = (unsigned int*)(bars + 24);
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+  volatile unsigned int* turn = (volatile unsigned int*)(tmem_holder + 2);
+  volatile unsigned int* zero_word = (volatile unsigned int*)(tmem_holder + 3);
   const unsigned int bar0 = smem_u32(bars);
 #define BAR(i) (bar0 + 8u * (i))
 #if ATTN_TRACE
@@ -151,11 +153,13 @@ extern "C" __global__ void __launch_bounds__(320, 1)
 #endif
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 11; ++i) mbar_init(BAR(i), 1);
+    for (int i = 0; i < 11; ++i) mbar_init(BAR(i), (i >= 3 && i <= 4) || (i >= 7 && i <= 8) ? 2 : 1);   // the empties take one arrival per tile
     mbar_init(BAR(11), 4); mbar_init(BAR(12), 4);
     mbar_init(BAR(13), 1); mbar_init(BAR(14), 1);
     mbar_init(BAR(15), 4); mbar_init(BAR(16), 4);
     *abort_flag = 0;
+    *turn = 0;
+    *zero_word = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -193,94 +197,95 @@ extern "C" __global__ void __launch_bounds__(320, 1)
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    // One thread issues every MMA, tile 0 then tile 1 in turn: that order keeps the two tiles half
-    // a period apart, so one tile's softmax runs (and has the special-function unit to itself)
-    // while the other tile's MMAs execute.  The tensor pipe takes MMAs no faster than this thread
-    // hands them over, so everything else it does (barrier probes, fences, commits) is kept short
-    // and the operand barriers, normally long complete, are probed before the wait for P.
+  } else if (warp == 1 || warp == 10) {
+    // ---------------- MMA issuers: warp 1 serves tile 0, warp 10 tile 1 ----------------
+    // One thread per tile issues that tile's MMAs.  The tensor pipe takes MMAs no faster than a
+    // thread hands them over, and a thread's barrier probes, fences and commits cost it tens to
+    // hundreds of cycles each; with two issuers those run while the other tile's MMAs are issued.
+    // The issuers take strict turns (a counter in shared memory): tile 0's PV and next S, then
+    // tile 1's, and so on.  The turns keep the two tiles half a period apart, so that one tile's
+    // softmax has the special-function unit to itself while the other tile's MMAs execute; they
+    // are a matter of speed only, every data dependence goes through the mbarriers.
     if (lane == 0) {
+      const int t = warp == 1 ? 0 : 1;
+      const int n_t = t == 0 ? n0 : n1;
       // S = Q K^T: A, B K-major, M = N = 128.  O += P V: A from TMEM, B = V with dim contiguous (N-major).
       const unsigned int idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned int)(TILE >> 3) << 17) | ((unsigned int)(TILE >> 4) << 24);
       const unsigned int idesc_o = idesc_s | (1u << 16);
-      const unsigned long long q_desc0 = smem_desc(smem_u32(q_smem), 16, 1024);
-      const unsigned long long q_desc1 = smem_desc(smem_u32(q_smem + TILE_BYTES), 16, 1024);
+      const unsigned int s_tmem = tmem_base + t * TILE, o_tmem = tmem_base + 2 * TILE + t * TILE;
+      const unsigned long long q_desc = smem_desc(smem_u32(q_smem + t * TILE_BYTES), 16, 1024);
       bool ok = true;
       auto wait_kv = [&](int base, int j) {
         return mbar_wait(BAR(base + j % KV_STAGES), (unsigned int)((j / KV_STAGES) & 1), abort_flag);
       };
+      auto wait_turn = [&](unsigned int want) {
+        for (unsigned int i = 0; i < SPIN_LIMIT; ++i) {
+          if (*turn == want) return true;
+          if ((i & 255u) == 255u && *abort_flag) return false;
+        }
+        *abort_flag = 1;
+        return false;
+      };
       // descriptors advance by adding to their 14-bit address field (16-byte units)
-      auto issue_s = [&](int t, int j) {
+      auto issue_s = [&](int j) {
         const unsigned long long k_desc = smem_desc(smem_u32(k_smem + (j % KV_STAGES) * TILE_BYTES), 16, 1024);
-        const unsigned long long q_desc = t == 0 ? q_desc0 : q_desc1;
 #pragma unroll
         for (int k = 0; k < HEAD_DIM / 16; ++k) {
           const unsigned long long off = (unsigned long long)(((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4);
-          tc_mma_ss(tmem_base + t * TILE, q_desc + off, k_desc + off, idesc_s, k > 0 ? 1u : 0u);
+          tc_mma_ss(s_tmem, q_desc + off, k_desc + off, idesc_s, k > 0 ? 1u : 0u);
         }
         tc_commit(BAR(9 + t));
+        tc_commit(BAR(3 + j % KV_STAGES));   // K stage free (one arrival per tile)
       };
-      auto issue_pv_part = [&](int t, int j, int k0) {
+      auto issue_pv_part = [&](int j, int k0) {
         const unsigned long long v_desc = smem_desc(smem_u32(v_smem + (j % KV_STAGES) * TILE_BYTES), HALF_BYTES, 1024);
 #pragma unroll
         for (int k = k0; k < k0 + TILE / 32; ++k)
-          tc_mma_ts(tmem_base + 2 * TILE + t * TILE, tmem_base + t * TILE + k * 8,
-                    v_desc + (unsigned long long)((k * 16 * 128) >> 4), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          tc_mma_ts(o_tmem, s_tmem + k * 8, v_desc + (unsigned long long)((k * 16 * 128) >> 4), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
       };
-      // O_t += P_t V once P_t is in TMEM (in two halves of 64 keys when the softmax hands them over so)
-      auto issue_pv = [&](int t, int j) {
-        const unsigned int ph = (unsigned int)(j & 1);
-        if (HALF_HANDOFF) {
-          if (!mbar_wait(BAR(15 + t), ph, abort_flag)) return false;
-          tc_fence_after();
-          issue_pv_part(t, j, 0);
-          if (!mbar_wait(BAR(11 + t), ph, abort_flag)) return false;
-          TR(0, j, t * 4 + 1)
-          tc_fence_after();
-          issue_pv_part(t, j, TILE / 32);
-        } else {
-          if (!mbar_wait(BAR(11 + t), ph, abort_flag)) return false;
-          TR(0, j, t * 4 + 1)
-          tc_fence_after();
-          issue_pv_part(t, j, 0);
-          issue_pv_part(t, j, TILE / 32);
-        }
-        tc_commit(BAR(13 + t));
-        TR(0, j, t * 4 + 2)
-        return true;
-      };
-      ok = mbar_wait(BAR(0), 0, abort_flag) && wait_kv(1, 0);
+      // turns: 0 tile 0's first S, 1 tile 1's first S, then 2 + 2 j + t for step j of tile t
+      ok = mbar_wait(BAR(0), 0, abort_flag) && wait_kv(1, 0) && wait_turn((unsigned int)t);
       if (ok) {
         tc_fence_after();
-        issue_s(0, 0);
-        issue_s(1, 0);
-        tc_commit(BAR(3));   // K stage 0 is free once both S MMAs have read it
+        issue_s(0);
+        *turn = (unsigned int)t + 1u;
       }
-      for (int j = 0; ok && j < n1; ++j) {
-        TR(0, j, 0)
-        // operands of this step: V(j) and K(j + 1)
-        if (!wait_kv(5, j) || (j + 1 < n1 && !wait_kv(1, j + 1))) { ok = false; break; }
-        if (j < n0) {
-          if (!issue_pv(0, j)) { ok = false; break; }
-          if (j + 1 < n0) {
-            issue_s(0, j + 1);
-            TR(0, j, 3)
-          }
+      for (int j = 0; ok && j < n_t; ++j) {
+        const unsigned int ph = (unsigned int)(j & 1);
+        const unsigned int my_turn = 2u + 2u * (unsigned int)j + (unsigned int)t;
+        const bool more = j + 1 < n_t;
+        TR(t * 3, j, 0)
+        // the operands first (they are normally long in place), then P, then the turn
+        if (!wait_kv(5, j) || (more && !wait_kv(1, j + 1))) { ok = false; break; }
+        if (!mbar_wait(BAR((HALF_HANDOFF ? 15 : 11) + t), ph, abort_flag)) { ok = false; break; }
+        TR(t * 3, j, 1)
+        if (!wait_turn(my_turn)) { ok = false; break; }
+        TR(t * 3, j, 2)
+        tc_fence_after();
+        issue_pv_part(j, 0);
+        if (HALF_HANDOFF) {
+          if (!mbar_wait(BAR(11 + t), ph, abort_flag)) { ok = false; break; }
+          TR(t * 3, j, 3)
+          tc_fence_after();
         }
-        if (!issue_pv(1, j)) { ok = false; break; }
-        tc_commit(BAR(7 + j % KV_STAGES));   // V stage free
-        if (j + 1 < n1) {
-          issue_s(1, j + 1);
-          tc_commit(BAR(3 + (j + 1) % KV_STAGES));   // K stage free
-          TR(0, j, 7)
-        }
+        issue_pv_part(j, TILE / 32);
+        tc_commit(BAR(13 + t));               // O_t holds blocks 0..j
+        tc_commit(BAR(7 + j % KV_STAGES));    // V stage free (one arrival per tile)
+        TR(t * 3, j, 4)
+        if (more) issue_s(j + 1);
+        TR(t * 3, j, 5)
+        *turn = my_turn + 1u;
 #if ATTN_TRACE
         if (blockIdx.x == 0 && j >= TRACE_J0 && j < TRACE_J0 + TRACE_N) {
           unsigned long long ns; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
-          trace[(3 * TRACE_N + j - TRACE_J0) * 8 + 0] = (unsigned int)ns;
+          trace[(t * 3 * TRACE_N + j - TRACE_J0) * 8 + 7] = (unsigned int)ns;
         }
 #endif
+      }
+      // causal programs: tile 1 has one more step, and its turn follows a turn of tile 0
+      if (ok && t == 0 && n1 > n0) {
+        const unsigned int my_turn = 2u + 2u * (unsigned int)n0;
+        if (wait_turn(my_turn)) *turn = my_turn + 1u;
       }
     }
   } else if (warp >= 2 && warp < 10) {
@@ -372,7 +377,8 @@ extern "C" __global__ void __launch_bounds__(320, 1)
       // 64 keys at a time.  A fixed share of the exponentials (POLY_SHARE of every 8 pairs of the
       // odd quarters) can run on the FMA pipe instead of the special-function unit.
       if (((TRACE_SOFTMAX >> 3) & 1) && row == 0) { TR(1 + t, j, 3) }
-      const unsigned long long c2 = pk2(SCALE_LOG2, SCALE_LOG2), nm2 = pk2(-m_run, -m_run);
+      const unsigned long long c2 = pk2(SCALE_LOG2, SCALE_LOG2);
+      unsigned long long nm2 = pk2(-m_run, -m_run);
       unsigned long long l2a = pk2(0.0f, 0.0f), l2b = l2a;
 #define EXP_QUARTER(R, COL0, OUT, AT, ACC, MASKED, POLY)                                     \
       _Pragma("unroll")                                                                      \
@@ -401,6 +407,10 @@ extern "C" __global__ void __launch_bounds__(320, 1)
         tc_fence_before();                                                                   \
         __syncwarp();                                                                        \
         if (lane == 0) mbar_arrive(BAR(15 + t));                                             \
+        /* the second half's arithmetic takes a word read after the arrival (always zero) as an  \
+           input, so that it cannot be scheduled ahead of the store and the arrival above */      \
+        const unsigned int z = *zero_word;                                                   \
+        nm2 = pk2u(__float_as_uint(-m_run) | z, __float_as_uint(-m_run) | z);                \
       }
       {
         unsigned int pa[32], pb[32];
@@ -408,17 +418,17 @@ extern "C" __global__ void __launch_bounds__(320, 1)
           EXP_QUARTER(r0, 0, pa, 0, l2a, true, false)
           EXP_QUARTER(r1, 32, pa, 16, l2b, true, false)
           tc_st32(s_addr, pa);
-          EXP_QUARTER(r2, 64, pb, 0, l2a, true, false)
           HALF_READY()
+          EXP_QUARTER(r2, 64, pb, 0, l2a, true, false)
           EXP_QUARTER(r3, 96, pb, 16, l2b, true, false)
           tc_st32(s_addr + 32, pb);
         } else {
           EXP_QUARTER(r0, 0, pa, 0, l2a, false, false)
           EXP_QUARTER(r1, 32, pa, 16, l2b, false, true)
           if (ABLATE != 3) tc_st32(s_addr, pa); else l2a = add2(l2a, pk2u(pa[0] ^ pa[5] ^ pa[17], pa[31] ^ pa[9]));
+          HALF_READY()
           if (((TRACE_SOFTMAX >> 4) & 1) && row == 0) { TR(1 + t, j, 4) }
           EXP_QUARTER(r2, 64, pb, 0, l2a, false, false)
-          HALF_READY()
           if (((TRACE_SOFTMAX >> 5) & 1) && row == 0) { TR(1 + t, j, 5) }
           EXP_QUARTER(r3, 96, pb, 16, l2b, false, true)
           if (ABLATE != 3) tc_st32(s_addr + 32, pb); else l2a = add2(l2a, pk2u(pb[0] ^ pb[5] ^ pb[17], pb[31] ^ pb[9]));
@@ -522,7 +532,7 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
   const long long items = (a.q_len / 256) * a.batch;
   if (items > 0x7fffffffll) throw PlanError("too many attention work items");
   l.grid[0] = static_cast<uint32_t>(items);
-  l.block[0] = 320;
+  l.block[0] = 384;
   l.dynamic_smem = 6 * 32768 + 1024 + 256 + (trace ? 4096 : 0);
   l.label = name;
   auto map = [&](int slot, int64_t seq) {

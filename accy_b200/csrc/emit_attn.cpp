@@ -4,18 +4,24 @@
 // flash.zig:330-604: f32 only, head dim 64, non-causal, 32x32 tiles of scalar FMAs) and its
 // library SDPA (src/kernel/library/attention.zig:389-441) with a tcgen05 kernel for bf16,
 // head dim 128, optional causal mask, any number of leading batch axes:
-//   * one CTA owns 256 consecutive queries of one (batch, head) as two 128-row tiles; K/V blocks
-//     of 128 keys stream through a TMA ring and are shared by both tiles;
+//   * a work item is 256 consecutive queries of one (batch, head), handled as two 128-row tiles;
+//     K/V blocks of 128 keys stream through a TMA ring and are shared by both tiles;
+//   * the kernel is persistent: one CTA per SM takes work items from a counter in global memory
+//     (all items of one (batch, head) next to each other, so its K and V stay in L2; heaviest
+//     first).  The TMA producer and the MMA issuers run ahead into the next item while the softmax
+//     warps finish the current one, so the load latency, the pipeline fill and the epilogue of
+//     one item overlap its neighbours;
 //   * S = Q K^T and O += P V run on the tensor cores (tcgen05.mma, f32 accumulators in TMEM:
 //     S0, S1, O0, O1 = 4 x 128 columns); P is written back over S as bf16 and read by the second
 //     MMA straight from TMEM;
 //   * two softmax warpgroups (one per tile, one thread per query row, so row max and row sum need
-//     no shuffles) work in ping-pong with the MMA issuer: while one tile's softmax runs the
+//     no shuffles) work in ping-pong with the MMA issuers: while one tile's softmax runs the
 //     tensor cores serve the other tile;
 //   * online softmax in f32 in the log2 domain (ex2.approx of fma(s, scale*log2e, -m)); O is only
 //     rescaled when a row's running max grows by more than 2^8, so the rescale through TMEM is rare;
 //   * causal programs skip key blocks above the diagonal and mask only the diagonal block.
-// Every mbarrier wait is bounded; on expiry the kernel sets the device status word and returns.
+// Every wait is bounded; on expiry the kernel sets the device status word and returns.
+#include <algorithm>
 #include <cmath>
 #include <sstream>
 
@@ -37,7 +43,7 @@ void replaceAll(std::string& s, const std::string& from, const std::string& to) 
   }
 }
 
-const char* kAttentionTemplate = R"CUDA(
+const char* kAttentionHead = R"CUDA(
 #define SEQ_Q @SEQ_Q@
 #define SEQ_K @SEQ_K@
 #define BATCH @BATCH@
@@ -47,13 +53,12 @@ const char* kAttentionTemplate = R"CUDA(
 #define KV_STAGES 2
 #define TILE_BYTES (TILE * HEAD_DIM * 2)   // one 128 x 128 bf16 tile: two 64-wide boxes of 16 KB
 #define HALF_BYTES (TILE * 64 * 2)
+#define N_PAIRS (SEQ_Q / (2 * TILE))
+#define N_ITEMS (N_PAIRS * BATCH)
 #define SCALE_LOG2 @SCALE_LOG2@f
 #define RESCALE_THRESHOLD 8.0f
-#define POLY_SHARE @POLY_SHARE@   // of every 8 pairs in the second half of a 64-column group
+#define POLY_SHARE @POLY_SHARE@   // of every 8 pairs in the odd 32-column quarters
 #define HALF_HANDOFF @HALF_HANDOFF@   // P is handed to the MMA issuer 64 keys at a time
-#define ABLATE @ABLATE@
-#define BH_MAJOR @BH_MAJOR@
-#define ATTN_TRACE @TRACE@        // development aid: one CTA records clock stamps of its hand-offs and prints them
 #ifndef INFINITY
 #define INFINITY __int_as_float(0x7f800000)
 #endif
@@ -104,59 +109,63 @@ __device__ __forceinline__ void tc_st32(unsigned int taddr, const unsigned int* 
                : "memory");
 }
 
+// work item -> (batch, head) index, first query row, key blocks of tile 0 and of tile 1
+__device__ __forceinline__ void decode_item(int item, int& bh, int& q_row0, int& n0, int& n1) {
+  const int pair = N_PAIRS - 1 - item % N_PAIRS;   // heaviest query pairs first
+  bh = item / N_PAIRS;
+  q_row0 = pair * 2 * TILE;
+#if CAUSAL
+  n0 = q_row0 / TILE + 1;
+  n1 = n0 + 1;
+#else
+  n0 = SEQ_K / TILE;
+  n1 = n0;
+#endif
+}
+
+// barriers (index into bars[]; arrivals per phase in brackets when not 1)
+#define B_Q_FULL 0
+#define B_Q_EMPTY 1        // [2] both tiles' last S of the item has read Q
+#define B_K_FULL 2         // + stage
+#define B_K_EMPTY 4        // + stage [2] one arrival per tile
+#define B_V_FULL 6         // + stage
+#define B_V_EMPTY 8        // + stage [2]
+#define B_S_FULL 10        // + tile
+#define B_P_FULL 12        // + tile [4] one arrival per softmax warp
+#define B_PV_DONE 14       // + tile
+#define B_P_HALF 16        // + tile [4] the first 64 keys of P are in TMEM
+#define B_ITEM_FULL 18     // + slot: the next work item is published
+#define B_ITEM_EMPTY 20    // + slot [10] both MMA issuers and the eight softmax warps have read it
+#define N_BARS 22
+
 extern "C" __global__ void __launch_bounds__(384, 1)
 @KERNEL@(const __grid_constant__ TensorMap map_q, const __grid_constant__ TensorMap map_k,
-         const __grid_constant__ TensorMap map_v, unsigned short* __restrict__ O, int* __restrict__ status) {
+         const __grid_constant__ TensorMap map_v, unsigned short* __restrict__ O, int* __restrict__ status,
+         int* __restrict__ counters) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((unsigned long long)smem_raw + 1023ull) & ~1023ull);
-  // layout: Q tile 0, Q tile 1, K stages, V stages, barriers
+  // layout: Q tile 0, Q tile 1, K stages, V stages, barriers, a few control words
   unsigned char* q_smem = smem;
   unsigned char* k_smem = smem + 2 * TILE_BYTES;
   unsigned char* v_smem = k_smem + KV_STAGES * TILE_BYTES;
   unsigned long long* bars = (unsigned long long*)(v_smem + KV_STAGES * TILE_BYTES);
-  // bars: 0 q_full | 1..2 k_full | 3..4 k_empty | 5..6 v_full | 7..8 v_empty | 9..10 s_full | 11..12 p_full | 13..14 pv_done
-  //       15..16 p_half (the first 64 keys of P are in TMEM)
   unsigned int* tmem_holder = (unsigned int*)(bars + 24);
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
   volatile unsigned int* turn = (volatile unsigned int*)(tmem_holder + 2);
   volatile unsigned int* zero_word = (volatile unsigned int*)(tmem_holder + 3);
+  volatile int* item_ring = (volatile int*)(tmem_holder + 4);   // two slots
   const unsigned int bar0 = smem_u32(bars);
-#define BAR(i) (bar0 + 8u * (i))
-#if ATTN_TRACE
-  unsigned int* trace = (unsigned int*)(bars + 32);
-#define TRACE_SOFTMAX @TRACE_SM@
-#define TRACE_J0 8
-#define TRACE_N 6
-#define TR(role, j, e) if (blockIdx.x == 0 && (j) >= TRACE_J0 && (j) < TRACE_J0 + TRACE_N) trace[((role) * TRACE_N + (j) - TRACE_J0) * 8 + (e)] = (unsigned int)clock64();
-#else
-#define TRACE_SOFTMAX 0
-#define TR(role, j, e)
-#endif
+#define BAR(i) (bar0 + 8u * (unsigned int)(i))
   const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // work item: heaviest query pairs first
-  const int n_pairs = SEQ_Q / (2 * TILE);
-#if BH_MAJOR
-  // the CTAs of one (batch, head) are launched together so that its K and V stay in L2
-  const int pair = n_pairs - 1 - (int)(blockIdx.x % n_pairs);
-  const int bh = (int)(blockIdx.x / n_pairs);
-#else
-  const int pair = n_pairs - 1 - (int)(blockIdx.x / BATCH);
-  const int bh = (int)(blockIdx.x % BATCH);
-#endif
-  const int q_row0 = pair * 2 * TILE;
-  // key blocks each tile attends to
-#if CAUSAL
-  const int n0 = q_row0 / TILE + 1, n1 = n0 + 1;
-#else
-  const int n0 = SEQ_K / TILE, n1 = n0;
-#endif
-
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 11; ++i) mbar_init(BAR(i), (i >= 3 && i <= 4) || (i >= 7 && i <= 8) ? 2 : 1);   // the empties take one arrival per tile
-    mbar_init(BAR(11), 4); mbar_init(BAR(12), 4);
-    mbar_init(BAR(13), 1); mbar_init(BAR(14), 1);
-    mbar_init(BAR(15), 4); mbar_init(BAR(16), 4);
+    for (int i = 0; i < N_BARS; ++i) {
+      int count = 1;
+      if (i == B_Q_EMPTY || (i >= B_K_EMPTY && i < B_K_EMPTY + 2) || (i >= B_V_EMPTY && i < B_V_EMPTY + 2)) count = 2;
+      if ((i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_P_HALF && i < B_P_HALF + 2)) count = 4;
+      if (i >= B_ITEM_EMPTY) count = 10;
+      mbar_init(BAR(i), count);
+    }
     *abort_flag = 0;
     *turn = 0;
     *zero_word = 0;
@@ -173,31 +182,50 @@ extern "C" __global__ void __launch_bounds__(384, 1)
   // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t overwrites the first 64 columns of S_t
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- work distribution and TMA producer ----------------
+    // The first item is the CTA's own index; further ones come from the counter in global memory.
+    // Each item is published to the other warps through a two-slot ring; the K/V ring simply
+    // continues from one item into the next, so the next item's first blocks are fetched while
+    // the current item is still being computed.
     if (lane == 0) {
-      mbar_expect_tx(BAR(0), 2 * TILE_BYTES);
-      for (int t = 0; t < 2; ++t)
-        for (int h = 0; h < 2; ++h)
-          tma_load_3d(smem_u32(q_smem + t * TILE_BYTES + h * HALF_BYTES), &map_q, BAR(0), h * 64, q_row0 + t * TILE, bh);
-      bool ok = true;
-      for (int j = 0; ok && j < n1; ++j) {
-        const int stage = j % KV_STAGES;
-        const unsigned int ph = (unsigned int)((j / KV_STAGES) & 1);
-        if (!mbar_wait(BAR(3 + stage), ph ^ 1u, abort_flag)) { ok = false; break; }
-        if (ABLATE == 5 && j >= 2) mbar_arrive(BAR(1 + stage)); else {
-        mbar_expect_tx(BAR(1 + stage), TILE_BYTES);
-        for (int h = 0; h < 2; ++h)
-          tma_load_3d(smem_u32(k_smem + stage * TILE_BYTES + h * HALF_BYTES), &map_k, BAR(1 + stage), h * 64, j * TILE, bh);
+      int item = (int)blockIdx.x;
+      unsigned int g = 0;   // K/V blocks loaded so far
+      for (int it = 0;; ++it) {
+        const int slot = it & 1;
+        if (!mbar_wait(BAR(B_ITEM_EMPTY + slot), (unsigned int)((it >> 1) & 1) ^ 1u, abort_flag)) break;
+        item_ring[slot] = item;
+        mbar_arrive(BAR(B_ITEM_FULL + slot));
+        if (item >= N_ITEMS) break;
+        const int next = (int)gridDim.x + atomicAdd(counters, 1);
+        int bh, q_row0, n0, n1;
+        decode_item(item, bh, q_row0, n0, n1);
+        (void)n0;
+        if (!mbar_wait(BAR(B_Q_EMPTY), (unsigned int)(it & 1) ^ 1u, abort_flag)) break;
+        mbar_expect_tx(BAR(B_Q_FULL), 2 * TILE_BYTES);
+        for (int t = 0; t < 2; ++t)
+          for (int h = 0; h < 2; ++h)
+            tma_load_3d(smem_u32(q_smem + t * TILE_BYTES + h * HALF_BYTES), &map_q, BAR(B_Q_FULL), h * 64, q_row0 + t * TILE, bh);
+        bool ok = true;
+        for (int j = 0; j < n1; ++j, ++g) {
+          const unsigned int stage = g % KV_STAGES;
+          const unsigned int ph = (g / KV_STAGES) & 1u;
+          if (!mbar_wait(BAR(B_K_EMPTY + stage), ph ^ 1u, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(BAR(B_K_FULL + stage), TILE_BYTES);
+          for (int h = 0; h < 2; ++h)
+            tma_load_3d(smem_u32(k_smem + stage * TILE_BYTES + h * HALF_BYTES), &map_k, BAR(B_K_FULL + stage), h * 64, j * TILE, bh);
+          if (!mbar_wait(BAR(B_V_EMPTY + stage), ph ^ 1u, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(BAR(B_V_FULL + stage), TILE_BYTES);
+          for (int h = 0; h < 2; ++h)
+            tma_load_3d(smem_u32(v_smem + stage * TILE_BYTES + h * HALF_BYTES), &map_v, BAR(B_V_FULL + stage), h * 64, j * TILE, bh);
         }
-        if (!mbar_wait(BAR(7 + stage), ph ^ 1u, abort_flag)) { ok = false; break; }
-        if (ABLATE == 5 && j >= 2) mbar_arrive(BAR(5 + stage)); else {
-        mbar_expect_tx(BAR(5 + stage), TILE_BYTES);
-        for (int h = 0; h < 2; ++h)
-          tma_load_3d(smem_u32(v_smem + stage * TILE_BYTES + h * HALF_BYTES), &map_v, BAR(5 + stage), h * 64, j * TILE, bh);
-        }
+        if (!ok) break;
+        item = next;
       }
     }
   } else if (warp == 1 || warp == 10) {
+)CUDA";
+
+const char* kAttentionIssuer = R"CUDA(
     // ---------------- MMA issuers: warp 1 serves tile 0, warp 10 tile 1 ----------------
     // One thread per tile issues that tile's MMAs.  The tensor pipe takes MMAs no faster than a
     // thread hands them over, and a thread's barrier probes, fences and commits cost it tens to
@@ -208,16 +236,11 @@ extern "C" __global__ void __launch_bounds__(384, 1)
     // are a matter of speed only, every data dependence goes through the mbarriers.
     if (lane == 0) {
       const int t = warp == 1 ? 0 : 1;
-      const int n_t = t == 0 ? n0 : n1;
       // S = Q K^T: A, B K-major, M = N = 128.  O += P V: A from TMEM, B = V with dim contiguous (N-major).
       const unsigned int idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned int)(TILE >> 3) << 17) | ((unsigned int)(TILE >> 4) << 24);
       const unsigned int idesc_o = idesc_s | (1u << 16);
       const unsigned int s_tmem = tmem_base + t * TILE, o_tmem = tmem_base + 2 * TILE + t * TILE;
       const unsigned long long q_desc = smem_desc(smem_u32(q_smem + t * TILE_BYTES), 16, 1024);
-      bool ok = true;
-      auto wait_kv = [&](int base, int j) {
-        return mbar_wait(BAR(base + j % KV_STAGES), (unsigned int)((j / KV_STAGES) & 1), abort_flag);
-      };
       auto wait_turn = [&](unsigned int want) {
         for (unsigned int i = 0; i < SPIN_LIMIT; ++i) {
           if (*turn == want) return true;
@@ -226,231 +249,244 @@ extern "C" __global__ void __launch_bounds__(384, 1)
         *abort_flag = 1;
         return false;
       };
+      // g counts K/V blocks over all items, in step with the producer
+      auto wait_block = [&](int base, unsigned int g) {
+        return mbar_wait(BAR(base + g % KV_STAGES), (g / KV_STAGES) & 1u, abort_flag);
+      };
       // descriptors advance by adding to their 14-bit address field (16-byte units)
-      auto issue_s = [&](int j) {
-        const unsigned long long k_desc = smem_desc(smem_u32(k_smem + (j % KV_STAGES) * TILE_BYTES), 16, 1024);
+      auto issue_s = [&](unsigned int g, bool last_of_item) {
+        const unsigned long long k_desc = smem_desc(smem_u32(k_smem + (g % KV_STAGES) * TILE_BYTES), 16, 1024);
 #pragma unroll
         for (int k = 0; k < HEAD_DIM / 16; ++k) {
           const unsigned long long off = (unsigned long long)(((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4);
           tc_mma_ss(s_tmem, q_desc + off, k_desc + off, idesc_s, k > 0 ? 1u : 0u);
         }
-        tc_commit(BAR(9 + t));
-        tc_commit(BAR(3 + j % KV_STAGES));   // K stage free (one arrival per tile)
+        tc_commit(BAR(B_S_FULL + t));
+        tc_commit(BAR(B_K_EMPTY + g % KV_STAGES));   // K stage free (one arrival per tile)
+        if (last_of_item) tc_commit(BAR(B_Q_EMPTY));  // Q free (one arrival per tile)
       };
-      auto issue_pv_part = [&](int j, int k0) {
-        const unsigned long long v_desc = smem_desc(smem_u32(v_smem + (j % KV_STAGES) * TILE_BYTES), HALF_BYTES, 1024);
+      auto issue_pv_part = [&](unsigned int g, int k0, bool first_block) {
+        const unsigned long long v_desc = smem_desc(smem_u32(v_smem + (g % KV_STAGES) * TILE_BYTES), HALF_BYTES, 1024);
 #pragma unroll
         for (int k = k0; k < k0 + TILE / 32; ++k)
-          tc_mma_ts(o_tmem, s_tmem + k * 8, v_desc + (unsigned long long)((k * 16 * 128) >> 4), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          tc_mma_ts(o_tmem, s_tmem + k * 8, v_desc + (unsigned long long)((k * 16 * 128) >> 4), idesc_o, (!first_block || k > 0) ? 1u : 0u);
       };
-      // turns: 0 tile 0's first S, 1 tile 1's first S, then 2 + 2 j + t for step j of tile t
-      ok = mbar_wait(BAR(0), 0, abort_flag) && wait_kv(1, 0) && wait_turn((unsigned int)t);
-      if (ok) {
+      unsigned int g0 = 0;          // K/V blocks of earlier items
+      unsigned int done = 0;        // blocks this tile has handled so far (parity of its barriers)
+      unsigned int turn0 = 0;       // first turn of the current item
+      bool ok = true;
+      for (int it = 0; ok; ++it) {
+        const int slot = it & 1;
+        if (!mbar_wait(BAR(B_ITEM_FULL + slot), (unsigned int)((it >> 1) & 1), abort_flag)) break;
+        const int item = item_ring[slot];
+        mbar_arrive(BAR(B_ITEM_EMPTY + slot));
+        if (item >= N_ITEMS) break;
+        int bh, q_row0, n0, n1;
+        decode_item(item, bh, q_row0, n0, n1);
+        (void)bh; (void)q_row0;
+        const int n_t = t == 0 ? n0 : n1;
+        // turns of an item: 0 tile 0's first S, 1 tile 1's first S, then 2 + 2 j + t for step j of tile t
+        ok = mbar_wait(BAR(B_Q_FULL), (unsigned int)(it & 1), abort_flag) && wait_block(B_K_FULL, g0) && wait_turn(turn0 + (unsigned int)t);
+        if (!ok) break;
         tc_fence_after();
-        issue_s(0);
-        *turn = (unsigned int)t + 1u;
-      }
-      for (int j = 0; ok && j < n_t; ++j) {
-        const unsigned int ph = (unsigned int)(j & 1);
-        const unsigned int my_turn = 2u + 2u * (unsigned int)j + (unsigned int)t;
-        const bool more = j + 1 < n_t;
-        TR(t * 3, j, 0)
-        // the operands first (they are normally long in place), then P, then the turn
-        if (!wait_kv(5, j) || (more && !wait_kv(1, j + 1))) { ok = false; break; }
-        if (!mbar_wait(BAR((HALF_HANDOFF ? 15 : 11) + t), ph, abort_flag)) { ok = false; break; }
-        TR(t * 3, j, 1)
-        if (!wait_turn(my_turn)) { ok = false; break; }
-        TR(t * 3, j, 2)
-        tc_fence_after();
-        issue_pv_part(j, 0);
-        if (HALF_HANDOFF) {
-          if (!mbar_wait(BAR(11 + t), ph, abort_flag)) { ok = false; break; }
-          TR(t * 3, j, 3)
+        issue_s(g0, n_t == 1);
+        *turn = turn0 + (unsigned int)t + 1u;
+        for (int j = 0; j < n_t; ++j, ++done) {
+          const unsigned int ph = done & 1u;
+          const unsigned int my_turn = turn0 + 2u + 2u * (unsigned int)j + (unsigned int)t;
+          const unsigned int g = g0 + (unsigned int)j;
+          const bool more = j + 1 < n_t;
+          // the operands first (they are normally long in place), then P, then the turn
+          if (!wait_block(B_V_FULL, g) || (more && !wait_block(B_K_FULL, g + 1))) { ok = false; break; }
+          if (!mbar_wait(BAR((HALF_HANDOFF ? B_P_HALF : B_P_FULL) + t), ph, abort_flag)) { ok = false; break; }
+          if (!wait_turn(my_turn)) { ok = false; break; }
           tc_fence_after();
+          issue_pv_part(g, 0, j == 0);
+          if (HALF_HANDOFF) {
+            if (!mbar_wait(BAR(B_P_FULL + t), ph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+          }
+          issue_pv_part(g, TILE / 32, j == 0);
+          tc_commit(BAR(B_PV_DONE + t));               // O_t holds blocks 0..j of the item
+          tc_commit(BAR(B_V_EMPTY + g % KV_STAGES));   // V stage free (one arrival per tile)
+          if (more) issue_s(g + 1, j + 2 == n_t);
+          *turn = my_turn + 1u;
         }
-        issue_pv_part(j, TILE / 32);
-        tc_commit(BAR(13 + t));               // O_t holds blocks 0..j
-        tc_commit(BAR(7 + j % KV_STAGES));    // V stage free (one arrival per tile)
-        TR(t * 3, j, 4)
-        if (more) issue_s(j + 1);
-        TR(t * 3, j, 5)
-        *turn = my_turn + 1u;
-#if ATTN_TRACE
-        if (blockIdx.x == 0 && j >= TRACE_J0 && j < TRACE_J0 + TRACE_N) {
-          unsigned long long ns; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
-          trace[(t * 3 * TRACE_N + j - TRACE_J0) * 8 + 7] = (unsigned int)ns;
+        if (!ok) break;
+        // causal items: tile 1 has one more block.  Tile 0 releases that block's stages on its
+        // own behalf (once the block is in, i.e. the stage's previous round is over) and passes
+        // the turn on.
+        if (t == 0 && n1 > n0) {
+          const unsigned int g = g0 + (unsigned int)n0;
+          if (!wait_block(B_K_FULL, g)) break;
+          mbar_arrive(BAR(B_K_EMPTY + g % KV_STAGES));
+          if (!wait_block(B_V_FULL, g)) break;
+          mbar_arrive(BAR(B_V_EMPTY + g % KV_STAGES));
+          const unsigned int my_turn = turn0 + 2u + 2u * (unsigned int)n0;
+          if (!wait_turn(my_turn)) break;
+          *turn = my_turn + 1u;
         }
-#endif
-      }
-      // causal programs: tile 1 has one more step, and its turn follows a turn of tile 0
-      if (ok && t == 0 && n1 > n0) {
-        const unsigned int my_turn = 2u + 2u * (unsigned int)n0;
-        if (wait_turn(my_turn)) *turn = my_turn + 1u;
+        g0 += (unsigned int)n1;
+        turn0 += 2u + 2u * (unsigned int)n1;
       }
     }
+)CUDA";
+
+const char* kAttentionSoftmax = R"CUDA(
   } else if (warp >= 2 && warp < 10) {
     // ---------------- softmax + correction + epilogue: warps 2..5 tile 0, warps 6..9 tile 1 ----------------
     const int t = (warp - 2) >> 2;
     const unsigned int quarter = warp & 3u;
     const int row = (int)(quarter * 32 + lane);           // query row inside the tile
-    const int n_t = t == 0 ? n0 : n1;
     const unsigned int lane_base = (quarter * 32u) << 16;
     const unsigned int s_addr = tmem_base + lane_base + t * TILE;
     const unsigned int o_addr = tmem_base + lane_base + 2 * TILE + t * TILE;
-    float m_run = -INFINITY, l_run = 0.0f;
+    unsigned int done = 0;   // blocks this tile has handled so far (parity of its barriers)
     bool ok = true;
-    for (int j = 0; ok && j < n_t; ++j) {
-      if (((TRACE_SOFTMAX >> 0) & 1) && row == 0) { TR(1 + t, j, 0) }
-      if (!mbar_wait(BAR(9 + t), (unsigned int)(j & 1), abort_flag)) { ok = false; break; }
-      if (((TRACE_SOFTMAX >> 1) & 1) && row == 0) { TR(1 + t, j, 1) }
-      tc_fence_after();
-      const bool diagonal = CAUSAL && (j == n_t - 1);
-      // the whole score row (128 columns) is read once and stays in registers for the row max
-      // and for the exponentials; the four loads are in flight together
-      unsigned int r0[32], r1[32], r2[32], r3[32];
-      if (ABLATE == 4) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { r0[i] = (unsigned int)(j * 77 + i + row) << 18; r1[i] = r0[i] + 3; r2[i] = r0[i] + 2; r3[i] = r0[i] + 1; }
-      } else {
-      tc_ld32(s_addr, r0);
-      tc_ld32(s_addr + 32, r1);
-      tc_ld32(s_addr + 64, r2);
-      tc_ld32(s_addr + 96, r3);
-      tc_wait_ld();
-      }
-      if (((TRACE_SOFTMAX >> 2) & 1) && row == 0) { TR(1 + t, j, 2) }
-      // row max.  The scale is positive, so the max is taken over the raw scores and scaled once;
-      // four chains of three-input max fold the 128 values.
-      float m_blk;
-      {
-        float a = -INFINITY, b = -INFINITY, c = -INFINITY, d = -INFINITY;
-        if (diagonal) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            a = fmaxf(a, i > row ? -INFINITY : __uint_as_float(r0[i]));
-            b = fmaxf(b, 32 + i > row ? -INFINITY : __uint_as_float(r1[i]));
-            c = fmaxf(c, 64 + i > row ? -INFINITY : __uint_as_float(r2[i]));
-            d = fmaxf(d, 96 + i > row ? -INFINITY : __uint_as_float(r3[i]));
-          }
-        } else if (ABLATE == 2) {
-          a = b = c = d = 1.0f;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            a = max3(a, __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
-            b = max3(b, __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
-            c = max3(c, __uint_as_float(r2[i]), __uint_as_float(r2[i + 1]));
-            d = max3(d, __uint_as_float(r3[i]), __uint_as_float(r3[i + 1]));
-          }
-        }
-        m_blk = fmaxf(fmaxf(a, b), fmaxf(c, d)) * SCALE_LOG2;
-      }
-      if (j == 0) {
-        m_run = m_blk;
-      } else {
-        const float m_new = fmaxf(m_run, m_blk);
-        const bool need = (m_new - m_run) > RESCALE_THRESHOLD;
-        if (__any_sync(0xffffffffu, need)) {
-          const float factor = need ? fast_exp2(m_run - m_new) : 1.0f;
-          if (need) { m_run = m_new; l_run *= factor; }
-          // O of this tile is up to date once the previous P V product has completed
-          if (!mbar_wait(BAR(13 + t), (unsigned int)((j - 1) & 1), abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          // rare path: the first score registers serve as scratch and the scores are read again
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            tc_ld32(o_addr + c * 32, r0);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r0[i] = __float_as_uint(__uint_as_float(r0[i]) * factor);
-            tc_st32(o_addr + c * 32, r0);
-          }
-          tc_wait_st();
-          tc_ld32(s_addr, r0);
-          tc_ld32(s_addr + 32, r1);
-          tc_ld32(s_addr + 64, r2);
-          tc_ld32(s_addr + 96, r3);
-          tc_wait_ld();
-        }
-      }
-      // p = 2^(scale * s - m) as packed FMAs and ex2, packed row sums, bf16 pairs written over S
-      // 64 keys at a time.  A fixed share of the exponentials (POLY_SHARE of every 8 pairs of the
-      // odd quarters) can run on the FMA pipe instead of the special-function unit.
-      if (((TRACE_SOFTMAX >> 3) & 1) && row == 0) { TR(1 + t, j, 3) }
-      const unsigned long long c2 = pk2(SCALE_LOG2, SCALE_LOG2);
-      unsigned long long nm2 = pk2(-m_run, -m_run);
-      unsigned long long l2a = pk2(0.0f, 0.0f), l2b = l2a;
-#define EXP_QUARTER(R, COL0, OUT, AT, ACC, MASKED, POLY)                                     \
-      _Pragma("unroll")                                                                      \
-      for (int i = 0; i < 32; i += 2) {                                                      \
-        const unsigned long long x2 = fma2(pk2u(R[i], R[i + 1]), c2, nm2);                   \
-        float p0, p1;                                                                        \
-        if (!(MASKED) && (POLY) && ((i >> 1) & 7) < POLY_SHARE) {                            \
-          poly_exp2_pair(x2, p0, p1);                                                        \
-        } else {                                                                             \
-          upk2(x2, p0, p1);                                                                  \
-          if (MASKED) {                                                                      \
-            if ((COL0) + i > row) p0 = -INFINITY;                                            \
-            if ((COL0) + i + 1 > row) p1 = -INFINITY;                                        \
-          }                                                                                  \
-          if (ABLATE != 1) {                                                                 \
-          p0 = fast_exp2(p0);                                                                \
-          p1 = fast_exp2(p1);                                                                \
-          }                                                                                  \
-        }                                                                                    \
-        ACC = add2(ACC, pk2(p0, p1));                                                        \
-        OUT[(AT) + (i >> 1)] = pack_bf16(p0, p1);                                            \
-      }
-#define HALF_READY()                                                                         \
-      if (HALF_HANDOFF) {                                                                    \
-        tc_wait_st();                                                                        \
-        tc_fence_before();                                                                   \
-        __syncwarp();                                                                        \
-        if (lane == 0) mbar_arrive(BAR(15 + t));                                             \
-        /* the second half's arithmetic takes a word read after the arrival (always zero) as an  \
-           input, so that it cannot be scheduled ahead of the store and the arrival above */      \
-        const unsigned int z = *zero_word;                                                   \
-        nm2 = pk2u(__float_as_uint(-m_run) | z, __float_as_uint(-m_run) | z);                \
-      }
-      {
-        unsigned int pa[32], pb[32];
-        if (diagonal) {
-          EXP_QUARTER(r0, 0, pa, 0, l2a, true, false)
-          EXP_QUARTER(r1, 32, pa, 16, l2b, true, false)
-          tc_st32(s_addr, pa);
-          HALF_READY()
-          EXP_QUARTER(r2, 64, pb, 0, l2a, true, false)
-          EXP_QUARTER(r3, 96, pb, 16, l2b, true, false)
-          tc_st32(s_addr + 32, pb);
-        } else {
-          EXP_QUARTER(r0, 0, pa, 0, l2a, false, false)
-          EXP_QUARTER(r1, 32, pa, 16, l2b, false, true)
-          if (ABLATE != 3) tc_st32(s_addr, pa); else l2a = add2(l2a, pk2u(pa[0] ^ pa[5] ^ pa[17], pa[31] ^ pa[9]));
-          HALF_READY()
-          if (((TRACE_SOFTMAX >> 4) & 1) && row == 0) { TR(1 + t, j, 4) }
-          EXP_QUARTER(r2, 64, pb, 0, l2a, false, false)
-          if (((TRACE_SOFTMAX >> 5) & 1) && row == 0) { TR(1 + t, j, 5) }
-          EXP_QUARTER(r3, 96, pb, 16, l2b, false, true)
-          if (ABLATE != 3) tc_st32(s_addr + 32, pb); else l2a = add2(l2a, pk2u(pb[0] ^ pb[5] ^ pb[17], pb[31] ^ pb[9]));
-        }
-      }
-      {
-        float s0, s1;
-        upk2(add2(l2a, l2b), s0, s1);
-        l_run += s0 + s1;
-      }
-      if (((TRACE_SOFTMAX >> 6) & 1) && row == 0) { TR(1 + t, j, 6) }
-      tc_wait_st();
-      tc_fence_before();
+    for (int it = 0; ok; ++it) {
+      const int slot = it & 1;
+      if (!mbar_wait(BAR(B_ITEM_FULL + slot), (unsigned int)((it >> 1) & 1), abort_flag)) break;
+      const int item = item_ring[slot];
       __syncwarp();
-      if (lane == 0) mbar_arrive(BAR(11 + t));
-      if (((TRACE_SOFTMAX >> 7) & 1) && row == 0) { TR(1 + t, j, 7) }
-#if ATTN_TRACE
-      if (!((TRACE_SOFTMAX >> 7) & 1) && lane == 0) { TR(1 + t, j, 4 + (int)quarter) }
-#endif
-    }
-    // epilogue: O / l -> bf16 -> global
-    if (ok && mbar_wait(BAR(13 + t), (unsigned int)((n_t - 1) & 1), abort_flag)) {
+      if (lane == 0) mbar_arrive(BAR(B_ITEM_EMPTY + slot));
+      if (item >= N_ITEMS) break;
+      int bh, q_row0, n0, n1;
+      decode_item(item, bh, q_row0, n0, n1);
+      const int n_t = t == 0 ? n0 : n1;
+      float m_run = -INFINITY, l_run = 0.0f;
+      for (int j = 0; ok && j < n_t; ++j, ++done) {
+        if (!mbar_wait(BAR(B_S_FULL + t), done & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const bool diagonal = CAUSAL && (j == n_t - 1);
+        // the whole score row (128 columns) is read once and stays in registers for the row max
+        // and for the exponentials; the four loads are in flight together
+        unsigned int r0[32], r1[32], r2[32], r3[32];
+        tc_ld32(s_addr, r0);
+        tc_ld32(s_addr + 32, r1);
+        tc_ld32(s_addr + 64, r2);
+        tc_ld32(s_addr + 96, r3);
+        tc_wait_ld();
+        // row max.  The scale is positive, so the max is taken over the raw scores and scaled
+        // once; four chains of three-input max fold the 128 values.
+        float m_blk;
+        {
+          float a = -INFINITY, b = -INFINITY, c = -INFINITY, d = -INFINITY;
+          if (diagonal) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              a = fmaxf(a, i > row ? -INFINITY : __uint_as_float(r0[i]));
+              b = fmaxf(b, 32 + i > row ? -INFINITY : __uint_as_float(r1[i]));
+              c = fmaxf(c, 64 + i > row ? -INFINITY : __uint_as_float(r2[i]));
+              d = fmaxf(d, 96 + i > row ? -INFINITY : __uint_as_float(r3[i]));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              a = max3(a, __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
+              b = max3(b, __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
+              c = max3(c, __uint_as_float(r2[i]), __uint_as_float(r2[i + 1]));
+              d = max3(d, __uint_as_float(r3[i]), __uint_as_float(r3[i + 1]));
+            }
+          }
+          m_blk = fmaxf(fmaxf(a, b), fmaxf(c, d)) * SCALE_LOG2;
+        }
+        if (j == 0) {
+          m_run = m_blk;
+        } else {
+          const float m_new = fmaxf(m_run, m_blk);
+          const bool need = (m_new - m_run) > RESCALE_THRESHOLD;
+          if (__any_sync(0xffffffffu, need)) {
+            const float factor = need ? fast_exp2(m_run - m_new) : 1.0f;
+            if (need) { m_run = m_new; l_run *= factor; }
+            // O of this tile is up to date once the previous P V product has completed
+            if (!mbar_wait(BAR(B_PV_DONE + t), (done - 1u) & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            // rare path: the first score registers serve as scratch and the scores are read again
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              tc_ld32(o_addr + c * 32, r0);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r0[i] = __float_as_uint(__uint_as_float(r0[i]) * factor);
+              tc_st32(o_addr + c * 32, r0);
+            }
+            tc_wait_st();
+            tc_ld32(s_addr, r0);
+            tc_ld32(s_addr + 32, r1);
+            tc_ld32(s_addr + 64, r2);
+            tc_ld32(s_addr + 96, r3);
+            tc_wait_ld();
+          }
+        }
+        // p = 2^(scale * s - m) as packed FMAs and ex2, packed row sums, bf16 pairs written over S
+        // 64 keys at a time.  A fixed share of the exponentials (POLY_SHARE of every 8 pairs of
+        // the odd quarters) can run on the FMA pipe instead of the special-function unit.
+        const unsigned long long c2 = pk2(SCALE_LOG2, SCALE_LOG2);
+        unsigned long long nm2 = pk2(-m_run, -m_run);
+        unsigned long long l2a = pk2(0.0f, 0.0f), l2b = l2a;
+#define EXP_QUARTER(R, COL0, OUT, AT, ACC, MASKED, POLY)                                     \
+        _Pragma("unroll")                                                                    \
+        for (int i = 0; i < 32; i += 2) {                                                    \
+          const unsigned long long x2 = fma2(pk2u(R[i], R[i + 1]), c2, nm2);                 \
+          float p0, p1;                                                                      \
+          if (!(MASKED) && (POLY) && ((i >> 1) & 7) < POLY_SHARE) {                          \
+            poly_exp2_pair(x2, p0, p1);                                                      \
+          } else {                                                                           \
+            upk2(x2, p0, p1);                                                                \
+            if (MASKED) {                                                                    \
+              if ((COL0) + i > row) p0 = -INFINITY;                                          \
+              if ((COL0) + i + 1 > row) p1 = -INFINITY;                                      \
+            }                                                                                \
+            p0 = fast_exp2(p0);                                                              \
+            p1 = fast_exp2(p1);                                                              \
+          }                                                                                  \
+          ACC = add2(ACC, pk2(p0, p1));                                                      \
+          OUT[(AT) + (i >> 1)] = pack_bf16(p0, p1);                                          \
+        }
+        // The second half's arithmetic takes a word read after the arrival (always zero) as an
+        // input, so that it cannot be scheduled ahead of the first half's store and arrival.
+#define HALF_READY()                                                                         \
+        if (HALF_HANDOFF) {                                                                  \
+          tc_wait_st();                                                                      \
+          tc_fence_before();                                                                 \
+          __syncwarp();                                                                      \
+          if (lane == 0) mbar_arrive(BAR(B_P_HALF + t));                                     \
+          const unsigned int z = *zero_word;                                                 \
+          nm2 = pk2u(__float_as_uint(-m_run) | z, __float_as_uint(-m_run) | z);              \
+        }
+        {
+          unsigned int pa[32], pb[32];
+          if (diagonal) {
+            EXP_QUARTER(r0, 0, pa, 0, l2a, true, false)
+            EXP_QUARTER(r1, 32, pa, 16, l2b, true, false)
+            tc_st32(s_addr, pa);
+            HALF_READY()
+            EXP_QUARTER(r2, 64, pb, 0, l2a, true, false)
+            EXP_QUARTER(r3, 96, pb, 16, l2b, true, false)
+            tc_st32(s_addr + 32, pb);
+          } else {
+            EXP_QUARTER(r0, 0, pa, 0, l2a, false, false)
+            EXP_QUARTER(r1, 32, pa, 16, l2b, false, true)
+            tc_st32(s_addr, pa);
+            HALF_READY()
+            EXP_QUARTER(r2, 64, pb, 0, l2a, false, false)
+            EXP_QUARTER(r3, 96, pb, 16, l2b, false, true)
+            tc_st32(s_addr + 32, pb);
+          }
+        }
+        {
+          float s0, s1;
+          upk2(add2(l2a, l2b), s0, s1);
+          l_run += s0 + s1;
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(B_P_FULL + t));
+      }
+      if (!ok) break;
+      // epilogue: O / l -> bf16 -> global, once the item's last P V product has completed
+      if (!mbar_wait(BAR(B_PV_DONE + t), (done - 1u) & 1u, abort_flag)) break;
       tc_fence_after();
       const float inv = 1.0f / l_run;
       unsigned short* orow = O + ((long long)bh * SEQ_Q + q_row0 + t * TILE + row) * HEAD_DIM;
@@ -468,26 +504,30 @@ extern "C" __global__ void __launch_bounds__(384, 1)
                               pack_bf16(__uint_as_float(r[q * 8 + 6]) * inv, __uint_as_float(r[q * 8 + 7]) * inv));
         }
       }
+      // the next item's first P V overwrites O: its P hand-over below comes after these loads
+      tc_fence_before();
     }
   }
+)CUDA";
 
+const char* kAttentionTail = R"CUDA(
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicExch(status, 2);
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
   }
   tc_fence_before();
   __syncthreads();
-#if ATTN_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    for (int role = 0; role < 4; ++role)
-      for (int j = 0; j < TRACE_N; ++j) {
-        const unsigned int* e = trace + (role * TRACE_N + j) * 8;
-        printf("TRACE role %d j %d : %u %u %u %u %u %u %u %u\n", role, TRACE_J0 + j, e[0], e[1], e[2], e[3], e[4], e[5], e[6], e[7]);
-      }
-  }
-#endif
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(512) : "memory");
+  }
+  // the last CTA to leave clears the work counter for the next launch
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(counters + 1, 1) == (int)gridDim.x - 1) {
+      counters[0] = 0;
+      counters[1] = 0;
+      __threadfence();
+    }
   }
 }
 )CUDA";
@@ -497,7 +537,7 @@ extern "C" __global__ void __launch_bounds__(384, 1)
 void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, const ScheduleOverrides& ov) {
   if (a.head_dim != 128 || a.q_len % 256 != 0 || a.k_len % 128 != 0)
     throw PlanError("attention shape not covered by the fused kernel");
-  std::string src = std::string(kConvertPrelude) + kTcPreludeShared + kAttentionTemplate;
+  std::string src = std::string(kConvertPrelude) + kTcPreludeShared + kAttentionHead + kAttentionIssuer + kAttentionSoftmax + kAttentionTail;
   std::ostringstream scale;
   scale.precision(9);
   scale << std::scientific << static_cast<double>(a.scale) * 1.4426950408889634;
@@ -507,20 +547,14 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
   replaceAll(src, "@BATCH@", std::to_string(a.batch));
   replaceAll(src, "@CAUSAL@", a.causal ? "1" : "0");
   replaceAll(src, "@SCALE_LOG2@", scale.str());
-  // share of exponentials moved to the FMA pipe: 0/8, 2/8, 4/8 or 8/8 of the pairs of one half,
-  // i.e. none, 1/8, 1/4 or 1/2 of all elements
-  // measured on the causal 4096 x 128 benchmark: none 847, 1/8 832, 1/4 812, 1/2 797 TFLOP/s, so the
-  // automatic choice is none (the kernel is bound by MMA/softmax hand-off latency, not by the
-  // special-function unit)
+  // Share of exponentials moved to the FMA pipe: 0/8, 2/8, 4/8 or 8/8 of the pairs of the odd
+  // quarters, i.e. none, 1/8, 1/4 or 1/2 of all elements.  Measured on the causal 4096 x 128
+  // benchmark every share above none was slower (the extra instructions compete with the MMA
+  // issuers for issue slots), so the automatic choice is none.
   const int poly_code = ov.attention_poly & 7;
   const int poly_share = poly_code == 2 ? 2 : poly_code == 3 ? 4 : poly_code == 4 ? 8 : 0;
   replaceAll(src, "@POLY_SHARE@", std::to_string(poly_share));
   replaceAll(src, "@HALF_HANDOFF@", (ov.attention_poly & 8) ? "0" : "1");
-  const bool trace = (ov.attention_poly & 16) != 0;
-  replaceAll(src, "@BH_MAJOR@", (ov.attention_poly & 256) ? "0" : "1");
-  replaceAll(src, "@ABLATE@", std::to_string((ov.attention_poly >> 5) & 7));
-  replaceAll(src, "@TRACE@", trace ? "1" : "0");
-  replaceAll(src, "@TRACE_SM@", std::to_string((ov.attention_poly >> 9) & 255));
   KernelSource ks;
   ks.name = name;
   ks.family = "attention";
@@ -531,9 +565,10 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
   l.kernel = static_cast<int>(plan.kernels.size()) - 1;
   const long long items = (a.q_len / 256) * a.batch;
   if (items > 0x7fffffffll) throw PlanError("too many attention work items");
-  l.grid[0] = static_cast<uint32_t>(items);
+  // persistent: one CTA per SM (the kernel's shared memory allows one), fewer when there is less work
+  l.grid[0] = static_cast<uint32_t>(std::min<long long>(items, ov.sm_count));
   l.block[0] = 384;
-  l.dynamic_smem = 6 * 32768 + 1024 + 256 + (trace ? 4096 : 0);
+  l.dynamic_smem = 6 * 32768 + 1024 + 256;
   l.label = name;
   auto map = [&](int slot, int64_t seq) {
     KernelArg m;
@@ -562,6 +597,15 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
   KernelArg st;
   st.slot = -2;
   l.args.push_back(st);
+  // work counter and exit counter: cleared at load time, left cleared by every launch
+  Slot counters;
+  counters.role = Slot::Scratch;
+  counters.bytes = 256;
+  counters.zero_init = true;
+  plan.slots.push_back(counters);
+  KernelArg ct;
+  ct.slot = static_cast<int>(plan.slots.size()) - 1;
+  l.args.push_back(ct);
   plan.launches.push_back(l);
 }
 

@@ -102,6 +102,7 @@ struct Slot {
   DType storage = DType::f32;
   uint32_t value = 0xffffffffu;  // program value the slot holds
   std::vector<uint8_t> payload;  // Constant: uploaded once at load time
+  bool zero_init = false;        // Scratch: cleared once at load time (kernels that use it leave it cleared)
 };
 
 struct KernelArg {

@@ -333,6 +333,7 @@ struct accy_b200_session {
       check(d.cuMemAlloc(&e.owned[s], slot.bytes ? slot.bytes : 1), "cuMemAlloc");
       if (slot.role == Slot::Constant)
         check(d.cuMemcpyHtoDAsync(e.owned[s], slot.payload.data(), slot.payload.size(), stream), "cuMemcpyHtoDAsync");
+      if (slot.zero_init && slot.bytes) check(d.cuMemsetD8Async(e.owned[s], 0, slot.bytes, stream), "cuMemsetD8Async");
     }
     check(d.cuStreamSynchronize(stream), "cuStreamSynchronize");
     check(d.cuEventCreate(&e.ev_begin, 0), "cuEventCreate");

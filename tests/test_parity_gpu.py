@@ -99,7 +99,9 @@ def test_dot_f32_known_answer(gpu_session):
 
 @pytest.mark.parametrize("batch,head,seq,dim,causal", [(1, 1, 48, 32, False), (1, 2, 64, 32, True), (2, 2, 256, 128, True),
                                                         (1, 2, 256, 128, False), (1, 3, 1024, 128, True),
-                                                        (2, 1, 512, 128, False), (1, 1, 2048, 128, True)])
+                                                        (2, 1, 512, 128, False), (1, 1, 2048, 128, True),
+                                                        # more work items than SMs: CTAs take several items each
+                                                        (4, 10, 1024, 128, True), (3, 26, 512, 128, False)])
 def test_attention_matches_f32_reference(gpu_session, batch, head, seq, dim, causal):
     cfg = configs.attention(batch, head, seq, dim, causal)
     inputs = cfg.make_inputs()
@@ -107,6 +109,22 @@ def test_attention_matches_f32_reference(gpu_session, batch, head, seq, dim, cau
     got = configs.bf16_bits_to_f32(outs[0].view(np.uint16))
     ref = configs.bf16_bits_to_f32(oracle.run(program.wire, inputs, mode="wide")[0]).reshape(-1)
     assert rel_err_bf16(got, ref) < 2e-2
+
+
+def test_attention_repeated_launches_agree(gpu_session):
+    """The persistent attention kernel hands out work through a device counter that every launch
+    must leave cleared: three launches of one compiled program give the same bytes."""
+    cfg = configs.attention(2, 40, 512, 128, True)   # 160 work items
+    inputs = cfg.make_inputs()
+    compiled = gpu_session.compile(cfg.program())
+    results = []
+    for _ in range(3):
+        out = np.zeros(compiled.output_descriptors()[0].byte_size, np.uint8)
+        gpu_session.invoke(compiled, inputs, [out])
+        results.append(out)
+    gpu_session.release(compiled)
+    assert results[0].any()
+    assert np.array_equal(results[0], results[1]) and np.array_equal(results[0], results[2])
 
 
 @pytest.mark.parametrize("tokens,d,h", [(8, 16, 32), (256, 256, 512), (128, 512, 1024)])

@@ -44,6 +44,7 @@ PROTOTYPES = {
     "accy_b200_session_describe": (c_u32, [c_p, c_u64, c_u32, c_u32, P(Descriptor)]),
     "accy_b200_session_invoke": (c_u32, [c_p, c_u64, P(c_p), P(c_size), c_u32, P(c_p), P(c_size), c_u32]),
     "accy_b200_session_invoke_device": (c_u32, [c_p, c_u64, P(c_u64), c_u32, P(c_u64), c_u32, c_p]),
+    "accy_b200_session_set_resident": (c_u32, [c_p, c_u64, c_u32, c_p, c_size]),
     "accy_b200_session_synchronize": (c_u32, [c_p, c_p]),
     "accy_b200_session_release": (c_u32, [c_p, c_u64]),
     "accy_b200_session_set_observer": (c_u32, [c_p, OBSERVER, c_p]),

@@ -42,6 +42,7 @@ struct Entry {
   std::vector<CUdeviceptr_t> owned;      // per slot: device memory owned by the session (0 = none)
   std::vector<CUdeviceptr_t> bound;      // per slot: pointer used by the current launch
   bool staging_ready = false;            // input/output slots have session-owned device buffers
+  std::vector<CUdeviceptr_t> resident;   // per parameter: device copy kept across invokes (0 = none)
   std::vector<std::vector<std::string>> names;  // descriptor name storage
   CUevent_t ev_begin = nullptr, ev_end = nullptr;
   bool timed = false;
@@ -254,7 +255,7 @@ struct accy_b200_session {
     const DriverTable& d = driver();
     uint64_t t0 = nowNs();
     for (size_t i = 0; i < P.input_sharded.size(); ++i) {
-      if (P.input_sharded[i]) continue;
+      if (P.input_sharded[i] || !inputs[i]) continue;
       size_t bytes = e.plan.slots[e.plan.input_slots[i]].bytes;
       if (bytes) check(d.cuMemcpyHtoDAsync(P.shared_inputs[i], inputs[i], bytes, P.streams[0]), "cuMemcpyHtoDAsync");
     }
@@ -268,10 +269,15 @@ struct accy_b200_session {
       for (size_t i = 0; i < P.input_sharded.size(); ++i) {
         int slot = x.plan.input_slots[i];
         if (!P.input_sharded[i]) {
-          x.bound[slot] = P.shared_inputs[i];
+          x.bound[slot] = inputs[i] ? P.shared_inputs[i] : e.resident[i];
           continue;
         }
         size_t bytes = x.plan.slots[slot].bytes;
+        if (!inputs[i] && bytes) {
+          // a resident input that carries the chunked axis: the chunk is a contiguous slice of it
+          x.bound[slot] = e.resident[i] + static_cast<CUdeviceptr_t>(c) * bytes;
+          continue;
+        }
         if (bytes)
           check(d.cuMemcpyHtoDAsync(x.owned[slot], static_cast<const char*>(inputs[i]) + static_cast<size_t>(c) * bytes, bytes, st),
                 "cuMemcpyHtoDAsync");
@@ -346,6 +352,8 @@ struct accy_b200_session {
       const DriverTable& d = driver();
       d.cuCtxSetCurrent(context);
       for (CUdeviceptr_t p : e.owned)
+        if (p) d.cuMemFree(p);
+      for (CUdeviceptr_t p : e.resident)
         if (p) d.cuMemFree(p);
       for (LoadedKernel& k : e.kernels)
         if (k.module) d.cuModuleUnload(k.module);
@@ -549,9 +557,10 @@ uint32_t accy_b200_session_invoke(accy_b200_session* s, uint64_t handle, const v
     std::vector<Range> ranges;
     for (uint32_t i = 0; i < input_count; ++i) {
       size_t want = e.plan.slots[e.plan.input_slots[i]].bytes;
-      if (!inputs || !input_sizes || input_sizes[i] != want || (!inputs[i] && want))
+      const bool kept = i < e.resident.size() && e.resident[i] != 0;
+      if (!inputs || !input_sizes || input_sizes[i] != want || (!inputs[i] && want && !kept))
         throw StatusError{ACCY_B200_INVALID_BUFFER, "input " + std::to_string(i) + " must be exactly " + std::to_string(want) + " bytes"};
-      ranges.push_back({static_cast<const char*>(inputs[i]), static_cast<const char*>(inputs[i]) + want});
+      if (inputs[i]) ranges.push_back({static_cast<const char*>(inputs[i]), static_cast<const char*>(inputs[i]) + want});
     }
     for (uint32_t j = 0; j < output_count; ++j) {
       size_t want = e.plan.slots[e.plan.output_slots[j]].bytes;
@@ -568,7 +577,13 @@ uint32_t accy_b200_session_invoke(accy_b200_session* s, uint64_t handle, const v
     const DriverTable& d = driver();
     s->check(d.cuCtxSetCurrent(s->context), "cuCtxSetCurrent");
     if (!e.pipeline.tried && !s->options.single_shot_invoke) s->buildPipeline(e);
-    if (e.pipeline.ready) {
+    bool pipelined = e.pipeline.ready;
+    for (uint32_t i = 0; pipelined && i < input_count; ++i) {
+      // chunks of a resident input are used in place, which needs every chunk to start aligned
+      size_t chunk = e.pipeline.lanes[0]->plan.slots[e.pipeline.lanes[0]->plan.input_slots[i]].bytes;
+      if (!inputs[i] && e.pipeline.input_sharded[i] && chunk % ACCY_B200_BUFFER_ALIGNMENT) pipelined = false;
+    }
+    if (pipelined) {
       s->runPipelined(e, inputs, outputs);
       return;
     }
@@ -578,6 +593,10 @@ uint32_t accy_b200_session_invoke(accy_b200_session* s, uint64_t handle, const v
     uint64_t t0 = nowNs();
     for (uint32_t i = 0; i < input_count; ++i) {
       int slot = e.plan.input_slots[i];
+      if (!inputs[i] && e.plan.slots[slot].bytes) {
+        e.bound[slot] = e.resident[i];   // kept on the device by set_resident
+        continue;
+      }
       if (e.plan.slots[slot].bytes)
         s->check(d.cuMemcpyHtoDAsync(e.owned[slot], inputs[i], e.plan.slots[slot].bytes, s->stream), "cuMemcpyHtoDAsync");
     }
@@ -620,6 +639,33 @@ uint32_t accy_b200_session_invoke_device(accy_b200_session* s, uint64_t handle, 
       e.bound[e.plan.output_slots[j]] = output_ptrs[j];
     }
     s->launchAll(e, stream ? static_cast<CUstream_t>(stream) : s->stream, true);
+  });
+}
+
+uint32_t accy_b200_session_set_resident(accy_b200_session* s, uint64_t handle, uint32_t input_index, const void* data,
+                                        size_t size) {
+  return guarded(s, [&] {
+    Entry& e = s->entryOf(handle);
+    if (input_index >= e.program.parameters.size()) throw StatusError{ACCY_B200_INVALID_BUFFER, "input index out of range"};
+    s->ensureDevice();
+    const DriverTable& d = driver();
+    s->check(d.cuCtxSetCurrent(s->context), "cuCtxSetCurrent");
+    e.resident.resize(e.program.parameters.size(), 0);
+    // no launch of this program may still be reading the copy that is replaced
+    s->check(d.cuStreamSynchronize(s->stream), "cuStreamSynchronize");
+    for (CUstream_t st : e.pipeline.streams) s->check(d.cuStreamSynchronize(st), "cuStreamSynchronize");
+    if (e.resident[input_index]) {
+      d.cuMemFree(e.resident[input_index]);
+      e.resident[input_index] = 0;
+    }
+    if (!data) return;
+    size_t want = e.plan.slots[e.plan.input_slots[input_index]].bytes;
+    if (size != want) throw StatusError{ACCY_B200_INVALID_BUFFER, "input " + std::to_string(input_index) + " must be exactly " + std::to_string(want) + " bytes"};
+    s->check(d.cuMemAlloc(&e.resident[input_index], want ? want : 1), "cuMemAlloc");
+    if (want) {
+      s->check(d.cuMemcpyHtoDAsync(e.resident[input_index], data, want, s->stream), "cuMemcpyHtoDAsync");
+      s->check(d.cuStreamSynchronize(s->stream), "cuStreamSynchronize");
+    }
   });
 }
 

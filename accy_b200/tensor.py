@@ -429,6 +429,9 @@ class Session:
         in_ptrs = (ctypes.c_void_p * max(1, len(inputs)))()
         in_sizes = (ctypes.c_size_t * max(1, len(inputs)))()
         for i, b in enumerate(inputs):
+            if b is None:   # an input kept on the device by set_resident
+                in_ptrs[i], in_sizes[i] = None, compiled.input_descriptors()[i].byte_size
+                continue
             addr, size, k = _buffer_address(b, False)
             in_ptrs[i], in_sizes[i] = addr, size
             keep.append(k)
@@ -440,6 +443,16 @@ class Session:
             keep.append(k)
         self._check(lib.accy_b200_session_invoke(self._h, compiled.handle, in_ptrs, in_sizes, len(inputs),
                                                  out_ptrs, out_sizes, len(outputs)))
+
+    def set_resident(self, compiled, index, data):
+        """Keeps input `index` of the program on the device across invokes (weights); later
+        `invoke` calls pass None for it.  `data` None drops the device copy."""
+        if data is None:
+            self._check(lib.accy_b200_session_set_resident(self._h, compiled.handle, index, None, 0))
+            return
+        addr, size, keep = _buffer_address(data, False)
+        self._check(lib.accy_b200_session_set_resident(self._h, compiled.handle, index, addr, size))
+        del keep
 
     def invoke_device(self, compiled, input_ptrs, output_ptrs, stream=None):
         ins = (ctypes.c_uint64 * max(1, len(input_ptrs)))(*input_ptrs)

@@ -115,6 +115,16 @@ uint32_t accy_b200_session_invoke_device(accy_b200_session* session, uint64_t ha
                                          const uint64_t* input_ptrs, uint32_t input_count,
                                          const uint64_t* output_ptrs, uint32_t output_count,
                                          void* stream);
+/* Keeps one input of a compiled program in device memory across invokes: `data` (exactly the
+ * descriptor's byte size) is copied to the device once; later accy_b200_session_invoke calls may
+ * pass NULL for that input (its size is still given) and the resident copy is used, so weights are
+ * not sent again with every call.  A non-NULL pointer in a later invoke overrides the resident copy
+ * for that call.  `data` == NULL drops the resident copy.  The reference keeps compiled programs
+ * and their buffers in Cpu / FragmentCompilerCache (src/tensor/execute.zig:14-51,
+ * src/executable/compiler.zig:39-153) but copies every input per launch; this call has no
+ * counterpart there. */
+uint32_t accy_b200_session_set_resident(accy_b200_session* session, uint64_t handle, uint32_t input_index,
+                                        const void* data, size_t size);
 uint32_t accy_b200_session_synchronize(accy_b200_session* session, void* stream);
 /* Session.release (session.zig:218-226): the handle is refused from then on. */
 uint32_t accy_b200_session_release(accy_b200_session* session, uint64_t handle);

@@ -339,6 +339,35 @@ def test_invoke_flow_on_the_fake_driver(fake_driver):
     session.deinit()
 
 
+def test_resident_inputs_are_copied_once(fake_driver):
+    """set_resident uploads an input once; invokes that pass None for it copy only the others,
+    a wrong size is refused, and dropping the copy makes None invalid again."""
+    session = tensor.Session(device=0)
+    compiled = session.compile(configs.mismatch(2, 16).program())
+    freq = np.array([2.5, 3.0], np.float32)
+    time = (0.25 * np.arange(16)).astype(np.float32)
+    sample = np.sin(3 * time).astype(np.float32)
+    out = np.zeros(2, np.float32)
+    with pytest.raises(tensor.SessionError) as err:
+        session.set_resident(compiled, 1, time[:8])
+    assert err.value.name == "invalid_buffer"
+    with pytest.raises(tensor.SessionError):
+        session.set_resident(compiled, 3, time)
+    copies = lib.accy_b200_test_fake_call_count(b"cuMemcpyHtoDAsync")
+    session.set_resident(compiled, 1, time)
+    session.set_resident(compiled, 2, sample)
+    assert lib.accy_b200_test_fake_call_count(b"cuMemcpyHtoDAsync") - copies == 2
+    copies = lib.accy_b200_test_fake_call_count(b"cuMemcpyHtoDAsync")
+    session.invoke(compiled, [freq, None, None], [out])
+    session.invoke(compiled, [freq, None, sample], [out])   # a pointer overrides the resident copy for that call
+    assert lib.accy_b200_test_fake_call_count(b"cuMemcpyHtoDAsync") - copies == 3
+    session.set_resident(compiled, 1, None)
+    with pytest.raises(tensor.SessionError) as err:
+        session.invoke(compiled, [freq, None, None], [out])
+    assert err.value.name == "invalid_buffer"
+    session.deinit()
+
+
 def test_failed_launch_poisons_the_session(fake_driver):
     session = tensor.Session(device=0)
     cfg = configs.mismatch(8, 16)

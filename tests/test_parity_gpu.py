@@ -172,6 +172,28 @@ def test_mismatch_full_size_sample(gpu_session):
     assert rel_err(got[:16], exact, 1e-6) < 1e-5
 
 
+@pytest.mark.parametrize("make,kept", [(lambda: configs.mlp(256, 256, 512), [1, 2, 3, 4, 5]),
+                                       (lambda: configs.mlp(4096, 2048, 4096), [1, 2, 3, 4, 5]),
+                                       (lambda: configs.softmax_layernorm(8192, 4096), [0])])
+def test_resident_inputs_give_the_same_bytes(gpu_session, make, kept):
+    """Inputs kept on the device by set_resident (weights; or, in the streamed invoke, an input
+    that carries the chunked axis and is then read in place) give the same output bytes."""
+    cfg = make()
+    inputs = cfg.make_inputs()
+    compiled = gpu_session.compile(cfg.program())
+    want = np.empty(compiled.output_descriptors()[0].byte_size, np.uint8)
+    gpu_session.invoke(compiled, inputs, [want])
+    for i in kept:
+        gpu_session.set_resident(compiled, i, inputs[i])
+    got = np.zeros_like(want)
+    gpu_session.invoke(compiled, [None if i in kept else a for i, a in enumerate(inputs)], [got])
+    assert np.array_equal(got, want)
+    got[:] = 0
+    gpu_session.invoke(compiled, [None if i in kept else a for i, a in enumerate(inputs)], [got])
+    assert np.array_equal(got, want)
+    gpu_session.release(compiled)
+
+
 @pytest.mark.parametrize("make", [lambda: configs.softmax_layernorm(8192, 4096), lambda: configs.mlp(4096, 2048, 4096),
                                   lambda: configs.attention(8, 4, 1024, 128)])
 def test_chunked_host_invoke_equals_single_shot(make):

@@ -7,6 +7,7 @@
 // kernels, the planned device slots and the launch list.  There is no CPU fallback anywhere:
 // without a CUDA device the session can only compile.
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -181,7 +182,10 @@ struct accy_b200_session {
     const std::string axis = out0.dims[0].name;
     ShardInfo info = analyseShardAxis(e.program, axis);
     if (!info.shardable || info.partial_sum) return;
-    int chunks = 16;
+    // more, smaller chunks shorten the unoverlapped first copy in and last copy out; below a few
+    // MiB per copy PCIe efficiency drops.  ACCY_B200_CHUNKS overrides the upper limit (experiments).
+    int chunks = 32;
+    if (const char* env = getenv("ACCY_B200_CHUNKS")) chunks = std::max(2, atoi(env));
     while (chunks > 1 && (info.extent % chunks != 0 || io_bytes / chunks < (16u << 20))) chunks /= 2;
     if (chunks < 2) return;
     try {

@@ -182,10 +182,10 @@ struct accy_b200_session {
     const std::string axis = out0.dims[0].name;
     ShardInfo info = analyseShardAxis(e.program, axis);
     if (!info.shardable || info.partial_sum) return;
-    // more, smaller chunks shorten the unoverlapped first copy in and last copy out; below a few
-    // MiB per copy PCIe efficiency drops.  ACCY_B200_CHUNKS overrides the upper limit (experiments).
-    int chunks = 32;
-    if (const char* env = getenv("ACCY_B200_CHUNKS")) chunks = std::max(2, atoi(env));
+    // 16 chunks at most: with 32 or 64 the end-to-end rate measured lower (C2 90 -> 89 -> 83 GB/s,
+    // attention 68 -> 59 TFLOP/s); the copies in and out already run at what PCIe gives in both
+    // directions at once
+    int chunks = 16;
     while (chunks > 1 && (info.extent % chunks != 0 || io_bytes / chunks < (16u << 20))) chunks /= 2;
     if (chunks < 2) return;
     try {

@@ -84,13 +84,17 @@ class Planner {
     std::sort(roots.rbegin(), roots.rend());
     for (uint32_t v : roots) {
       if (produced.count(v)) continue;
+      if (P.typeOf(v).elementCount() == 0) {   // nothing to compute
+        produced.insert(v);
+        continue;
+      }
       planOutputRoot(v);
     }
     // duplicate outputs and outputs that are plain inputs/constants: device-side copies
     for (size_t j = 0; j < P.outputs.size(); ++j) {
       int want = plan.output_slots[j];
       int have = out_slot_of[P.outputs[j]];
-      if (want != have) copies.push_back({have, want});
+      if (want != have && plan.slots[want].bytes) copies.push_back({have, want});
     }
     for (auto& c : copies) emitCopy(c.first, c.second);
     plan.summary = summary.str();
@@ -1072,12 +1076,63 @@ class Planner {
 
 }  // namespace
 
+// Programs with zero-extent axes (the reference's type rules allow them, src/tensor/type/dim.zig:178
+// refuses only negative extents).  A value without elements needs no kernel; the only way a value
+// WITH elements can depend on one without is a reduction over an empty axis (the fold from the init
+// value over nothing: the init value itself, reduction.zig:839-863) or a contraction over an empty
+// axis (zeros).  Those two are re-recorded as broadcasts of a scalar; everything else is replayed
+// unchanged, after which no kernel ever reads an empty value.
+static Program withoutEmptyFolds(const Program& p) {
+  Builder b(p.name);
+  std::vector<uint32_t> now(p.ops.size(), 0);
+  for (const Operation& op : p.ops) {
+    auto arg = [&](size_t i) { return now[op.operands[i]]; };
+    const bool empty = op.result.elementCount() == 0;
+    uint32_t made = 0;
+    switch (op.kind) {
+      case Kind::parameter: made = b.input(op.result.dtype, op.result.dims, /*authored=*/false); break;
+      case Kind::constant: made = b.constantBytes(op.result, op.payload.data(), op.payload.size()); break;
+      case Kind::iota: made = b.iotaTyped(op.result, op.axis); break;
+      case Kind::unary: made = b.unary(static_cast<Unary>(op.sub), arg(0)); break;
+      case Kind::binary: made = b.binary(static_cast<Binary>(op.sub), arg(0), arg(1)); break;
+      case Kind::compare: made = b.compare(static_cast<Compare>(op.sub), arg(0), arg(1)); break;
+      case Kind::select: made = b.select(arg(0), arg(1), arg(2)); break;
+      case Kind::broadcast_in_dim: made = b.broadcastTo(arg(0), op.result.dims, op.ints); break;
+      case Kind::reshape: made = b.reshapeTo(arg(0), op.result.dims); break;
+      case Kind::transpose: made = b.transposeBy(arg(0), op.ints); break;
+      case Kind::reduce:
+        if (!empty && p.typeOf(op.operands[0]).elementCount() == 0) made = b.broadcastTo(arg(1), op.result.dims, {});
+        else made = b.reduce(arg(0), arg(1), static_cast<Reducer>(op.sub), op.ints);
+        break;
+      case Kind::dot_general:
+        if (!empty && (p.typeOf(op.operands[0]).elementCount() == 0 || p.typeOf(op.operands[1]).elementCount() == 0)) {
+          std::vector<uint8_t> zero(dtypeSize(op.result.dtype), 0);
+          made = b.broadcastTo(b.constantBytes(Type{op.result.dtype, {}}, zero.data(), zero.size()), op.result.dims, {});
+        } else {
+          made = b.dotGeneralOp(arg(0), arg(1), op.ints, op.rhs_contract, op.lhs_batch, op.rhs_batch);
+        }
+        break;
+      default:
+        throw PlanError("operation kind not supported by the B200 target");
+    }
+    now[op.id] = made;
+  }
+  std::vector<uint32_t> outputs;
+  for (uint32_t o : p.outputs) outputs.push_back(now[o]);
+  return b.finish(outputs);
+}
+
 Plan planProgram(const Program& program, const ScheduleOverrides& overrides) {
   if (program.outputs.empty()) throw PlanError("program has no outputs");
+  bool has_empty = false;
   for (const Operation& op : program.ops) {
     if (op.result.dtype == DType::key) throw PlanError("key-typed values are not supported by the B200 target");
-    for (const Dim& d : op.result.dims)
-      if (d.extent == 0) throw PlanError("zero-extent axes are not supported by the B200 target");
+    for (const Dim& d : op.result.dims) has_empty |= d.extent == 0;
+  }
+  if (has_empty) {
+    const Program rewritten = withoutEmptyFolds(program);
+    Planner planner(rewritten, overrides);
+    return planner.run();
   }
   Planner planner(program, overrides);
   return planner.run();

@@ -111,3 +111,40 @@ def test_matches_oracle(gpu_session, name):
         err_ref = np.max(np.abs(want64 - ex64) / np.maximum(np.abs(ex64), floor))
         tol = 1e-12 if ty.dtype == "f64" else 1e-5
         assert err_gpu < tol + err_ref, (name, err_gpu, err_ref)
+
+
+# Zero-extent axes: the reference's type rules allow them (only negative extents are refused);
+# a fold over an empty axis gives the init value, a contraction over an empty axis gives zeros.
+EMPTY_CASES = {
+    "empty_elementwise": ([T.spec("f32", n=0)], lambda b, a: a[0].mul(a[0])),
+    "sum_over_empty_axis": ([T.spec("f32", r=4, c=0)], lambda b, a: a[0].sum("c")),
+    "max_over_empty_axis": ([T.spec("f32", r=4, c=0)], lambda b, a: a[0].max("c")),
+    "mean_then_arithmetic": ([T.spec("f32", r=3, c=0), T.spec("f32", r=3)], lambda b, a: a[0].sum("c").add(a[1]).exp()),
+    "empty_rows": ([T.spec("f32", r=0, c=8)], lambda b, a: a[0].sum("c")),
+    "empty_contraction": ([T.spec("f32", m=3, k=0), T.spec("f32", k=0, n=2)], lambda b, a: a[0].contract(a[1], "k")),
+    "empty_and_full_outputs": ([T.spec("f32", n=0), T.spec("f32", m=5)], lambda b, a: [a[0].neg(), a[1].mul(a[1])]),
+}
+
+
+@pytest.mark.parametrize("name", sorted(EMPTY_CASES))
+def test_zero_extent_programs_compile(cpu_session, name):
+    specs, body = EMPTY_CASES[name]
+    compiled = cpu_session.compile(tensor.define(name, specs, body))
+    sizes = [d.byte_size for d in compiled.output_descriptors()]
+    assert compiled.work()["launches"] == (0 if not any(sizes) else compiled.work()["launches"])
+    cpu_session.release(compiled)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(EMPTY_CASES))
+def test_zero_extent_programs_match_oracle(gpu_session, name):
+    specs, body = EMPTY_CASES[name]
+    program = tensor.define(name, specs, body)
+    inputs = make_inputs(specs, seed=7)
+    compiled = gpu_session.compile(program)
+    outs = [np.full(d.byte_size, 0xAB, np.uint8) for d in compiled.output_descriptors()]
+    gpu_session.invoke(compiled, inputs, outs)
+    gpu_session.release(compiled)
+    expected = oracle.run(program.wire, inputs, mode="ref")
+    for got, want in zip(outs, expected):
+        assert np.array_equal(got.view(np.float32), np.asarray(want, np.float32).reshape(-1))

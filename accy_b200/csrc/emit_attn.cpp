@@ -254,13 +254,16 @@ const char* kAttentionIssuer = R"CUDA(
         return mbar_wait(BAR(base + g % KV_STAGES), (g / KV_STAGES) & 1u, abort_flag);
       };
       // descriptors advance by adding to their 14-bit address field (16-byte units)
-      auto issue_s = [&](unsigned int g, bool last_of_item) {
+      auto issue_s_mmas = [&](unsigned int g) {
         const unsigned long long k_desc = smem_desc(smem_u32(k_smem + (g % KV_STAGES) * TILE_BYTES), 16, 1024);
 #pragma unroll
         for (int k = 0; k < HEAD_DIM / 16; ++k) {
           const unsigned long long off = (unsigned long long)(((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4);
           tc_mma_ss(s_tmem, q_desc + off, k_desc + off, idesc_s, k > 0 ? 1u : 0u);
         }
+      };
+      auto issue_s = [&](unsigned int g, bool last_of_item) {
+        issue_s_mmas(g);
         tc_commit(BAR(B_S_FULL + t));
         tc_commit(BAR(B_K_EMPTY + g % KV_STAGES));   // K stage free (one arrival per tile)
         if (last_of_item) tc_commit(BAR(B_Q_EMPTY));  // Q free (one arrival per tile)
@@ -307,10 +310,21 @@ const char* kAttentionIssuer = R"CUDA(
             tc_fence_after();
           }
           issue_pv_part(g, TILE / 32, j == 0);
+          // The next S goes out before this step's other commits: the tile's softmax waits for
+          // it, nothing waits as urgently for "O is up to date" or for the free V stage (a
+          // commit covers everything issued before it, so those two now also wait for S), and
+          // the other issuer gets the turn before this thread spends its ~55 cycles per commit.
+          if (more) {
+            issue_s_mmas(g + 1);
+            tc_commit(BAR(B_S_FULL + t));
+          }
+          *turn = my_turn + 1u;
           tc_commit(BAR(B_PV_DONE + t));               // O_t holds blocks 0..j of the item
           tc_commit(BAR(B_V_EMPTY + g % KV_STAGES));   // V stage free (one arrival per tile)
-          if (more) issue_s(g + 1, j + 2 == n_t);
-          *turn = my_turn + 1u;
+          if (more) {
+            tc_commit(BAR(B_K_EMPTY + (g + 1) % KV_STAGES));   // K stage free (one arrival per tile)
+            if (j + 2 == n_t) tc_commit(BAR(B_Q_EMPTY));       // Q free (one arrival per tile)
+          }
         }
         if (!ok) break;
         // causal items: tile 1 has one more block.  Tile 0 releases that block's stages on its

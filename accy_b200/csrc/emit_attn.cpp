@@ -210,13 +210,17 @@ extern "C" __global__ void __launch_bounds__(384, 1)
         int bh, q_row0, n0, n1;
         decode_item(item, bh, q_row0, n0, n1);
         (void)n0;
-        if (!mbar_wait(BAR(B_Q_EMPTY), (unsigned int)(it & 1) ^ 1u, abort_flag)) break;
-        mbar_expect_tx(BAR(B_Q_FULL), 2 * TILE_BYTES);
-        for (int t = 0; t < 2; ++t)
-          for (int h = 0; h < 2; ++h)
-            tma_load_3d(smem_u32(q_smem + t * TILE_BYTES + h * HALF_BYTES), &map_q, BAR(B_Q_FULL), h * 64, q_row0 + t * TILE, bh);
+        // The item's first K/V block goes first: its stages come free a step earlier than the Q
+        // tiles (which the previous item's last S still reads), so it is not held up behind Q.
         bool ok = true;
         for (int j = 0; j < n1; ++j, ++g) {
+          if (j == (n1 > 1 ? 1 : 0)) {
+            if (!mbar_wait(BAR(B_Q_EMPTY), (unsigned int)(it & 1) ^ 1u, abort_flag)) { ok = false; break; }
+            mbar_expect_tx(BAR(B_Q_FULL), 2 * TILE_BYTES);
+            for (int t = 0; t < 2; ++t)
+              for (int h = 0; h < 2; ++h)
+                tma_load_3d(smem_u32(q_smem + t * TILE_BYTES + h * HALF_BYTES), &map_q, BAR(B_Q_FULL), h * 64, q_row0 + t * TILE, bh);
+          }
           const unsigned int stage = g % KV_STAGES;
           const unsigned int ph = (g / KV_STAGES) & 1u;
           if (!mbar_wait(BAR(B_K_EMPTY + stage), ph ^ 1u, abort_flag)) { ok = false; break; }

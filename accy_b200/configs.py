@@ -127,14 +127,15 @@ def matmul(m=8192, n=8192, k=8192, seed=2):
     return Config("matmul", matmul_body, specs, "m", inputs, work, 2e-2, "bf16")
 
 
-def attention(batch=8, head=32, seq=4096, dim=128, causal=True, seed=3):
+def attention(batch=8, head=32, seq=4096, dim=128, causal=True, seed=3, keys=None):
+    keys = seq if keys is None else keys   # a different key length (non-causal only): cross attention
     def inputs():
         rng = np.random.default_rng(seed)
-        return [f32_to_bf16_bits(rng.standard_normal((batch, head, seq, dim), dtype=np.float32)) for _ in range(3)]
+        return [f32_to_bf16_bits(rng.standard_normal((batch, head, n, dim), dtype=np.float32)) for n in (seq, keys, keys)]
     specs = [T.spec("bf16", batch=batch, head=head, seq=seq, dim=dim),
-             T.spec("bf16", batch=batch, head=head, key=seq, dim=dim),
-             T.spec("bf16", batch=batch, head=head, key=seq, dim=dim)]
-    pairs = seq * (seq + 1) / 2.0 if causal else float(seq) * seq
+             T.spec("bf16", batch=batch, head=head, key=keys, dim=dim),
+             T.spec("bf16", batch=batch, head=head, key=keys, dim=dim)]
+    pairs = seq * (seq + 1) / 2.0 if causal else float(seq) * keys
     work = {"bytes": 4.0 * 2 * batch * head * seq * dim, "flops": 4.0 * dim * pairs * batch * head, "pairs": 0.0}
     body = make_attention_body(1.0 / math.sqrt(dim), causal)
     return Config("attention", body, specs, "batch", inputs, work, 2e-2, "bf16")

@@ -111,6 +111,19 @@ def test_attention_matches_f32_reference(gpu_session, batch, head, seq, dim, cau
     assert rel_err_bf16(got, ref) < 2e-2
 
 
+@pytest.mark.parametrize("seq,keys", [(256, 128), (512, 384), (256, 1152)])
+def test_cross_attention_key_lengths(gpu_session, seq, keys):
+    """Non-causal attention whose key length differs from the query length: a single key block
+    (the tile's first S is also its last), an odd number of blocks, more key blocks than queries."""
+    cfg = configs.attention(1, 3, seq, 128, False, keys=keys)
+    inputs = cfg.make_inputs()
+    program, outs = run_gpu(gpu_session, cfg, inputs)
+    assert "attention:" in gpu_session.compile(program).plan_summary()
+    got = configs.bf16_bits_to_f32(outs[0].view(np.uint16))
+    ref = configs.bf16_bits_to_f32(oracle.run(program.wire, inputs, mode="wide")[0]).reshape(-1)
+    assert rel_err_bf16(got, ref) < 2e-2
+
+
 def test_attention_repeated_launches_agree(gpu_session):
     """The persistent attention kernel hands out work through a device counter that every launch
     must leave cleared: three launches of one compiled program give the same bytes."""

@@ -113,6 +113,9 @@ __device__ __forceinline__ float fast_exp2(float x) { float y; asm("ex2.approx.f
 __device__ __forceinline__ unsigned int pack_bf16(float lo, float hi) {
   unsigned int r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r;
 }
+__device__ __forceinline__ unsigned int pack_f16(float lo, float hi) {
+  unsigned int r; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r;
+}
 // shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100): start address, leading
 // and stride byte offsets in 16-byte units
 __device__ __forceinline__ unsigned long long smem_desc(unsigned int addr, unsigned int lbo_bytes, unsigned int sbo_bytes) {
@@ -125,6 +128,7 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned int addr, unsig
 const char* kGemmTemplate = R"CUDA(
 #define BLOCK_M 128
 #define BLOCK_N @BLOCK_N@
+#define AB_FORMAT @AB_FORMAT@
 #define BLOCK_K 64
 #define STAGES @STAGES@
 #define M_TOTAL @M@ll
@@ -215,8 +219,9 @@ extern "C" __global__ void __launch_bounds__(192, 1)
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      // instruction descriptor: f32 accumulate, bf16 x bf16, A K-major, B major as given, N, M=128
-      const unsigned int idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned int)B_N_MAJOR << 16) |
+      // instruction descriptor: f32 accumulate, A and B format (0 = f16, 1 = bf16), A K-major, B major
+      // as given, N, M=128
+      const unsigned int idesc = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | ((unsigned int)B_N_MAJOR << 16) |
                                  ((unsigned int)(BLOCK_N >> 3) << 17) | ((unsigned int)(BLOCK_M >> 4) << 24);
       int stage = 0; unsigned int phase = 0;
       unsigned int it = 0;
@@ -313,16 +318,17 @@ void emitGemmTcgen05(const GemmOp& g, const std::string& name, Plan& plan, const
   const int block_n = (g.n % 256 == 0) ? 256 : 128;
   const int stages = block_n == 256 ? 4 : 6;
   const bool n_major = g.b_stride_n == 1 && g.n > 1;
-  if (g.out_dtype != DType::bf16 && g.out_dtype != DType::f32) throw PlanError("tcgen05 GEMM output must be bf16 or f32");
+  if (g.out_dtype != DType::bf16 && g.out_dtype != DType::f16 && g.out_dtype != DType::f32)
+    throw PlanError("tcgen05 GEMM output must be bf16, f16 or f32");
 
   std::ostringstream body;
   std::string result = emitEpilogueBody(g.epilogue, body, "          ", "acc", "bi", "mi", "ni", "");
   std::string epi = body.str();
-  // bf16 programs: hardware tanh/exp approximations are inside the 2e-2 tolerance
-  replaceAll(epi, "tanhf(", "fast_tanh(");
+  // bf16 programs: hardware tanh/exp approximations are inside the 2e-2 tolerance (f16 keeps tanhf)
+  if (g.in_dtype == DType::bf16) replaceAll(epi, "tanhf(", "fast_tanh(");
 
   std::string store;
-  if (g.out_dtype == DType::bf16) {
+  if (g.out_dtype == DType::bf16 || g.out_dtype == DType::f16) {
     store =
         "        {\n"
         "          uint4* dst = reinterpret_cast<uint4*>(crow + c * 32);\n"
@@ -341,7 +347,9 @@ void emitGemmTcgen05(const GemmOp& g, const std::string& name, Plan& plan, const
   }
 
   std::string src = std::string(kConvertPrelude) + kTcPrelude + kGemmTemplate;
+  if (g.out_dtype == DType::f16) replaceAll(store, "pack_bf16(", "pack_f16(");
   replaceAll(src, "@KERNEL@", name);
+  replaceAll(src, "@AB_FORMAT@", g.in_dtype == DType::f16 ? "0u" : "1u");
   replaceAll(src, "@BLOCK_N@", std::to_string(block_n));
   replaceAll(src, "@STAGES@", std::to_string(stages));
   replaceAll(src, "@M@", std::to_string(g.m));

@@ -829,7 +829,8 @@ class Planner {
     g.out_dtype = plan.slots[g.c_slot].storage;
     const bool aligned = g.m % 128 == 0 && g.n % 128 == 0 && g.k % 64 == 0 && g.a_stride_k == 1 &&
                          (g.b_stride_n == 1 || g.b_stride_k == 1);
-    g.tensor_core = g.in_dtype == DType::bf16 && g.b_dtype == DType::bf16 && aligned && !ov.force_simt_gemm && tcgen05Ready();
+    const bool half_inputs = (g.in_dtype == DType::bf16 && g.b_dtype == DType::bf16) || (g.in_dtype == DType::f16 && g.b_dtype == DType::f16);
+    g.tensor_core = half_inputs && aligned && !ov.force_simt_gemm && tcgen05Ready();
     std::string name = nextName(g.tensor_core ? "gemm_tc" : "gemm_simt");
     summary << "gemm: " << name << " batch=" << g.batch << " m=" << g.m << " n=" << g.n << " k=" << g.k
             << " in=" << dtypeName(g.in_dtype) << " out=" << dtypeName(g.out_dtype)

@@ -111,6 +111,34 @@ def test_attention_matches_f32_reference(gpu_session, batch, head, seq, dim, cau
     assert rel_err_bf16(got, ref) < 2e-2
 
 
+F16_PROGRAMS = {
+    # f16 is the 16-bit float the reference's own dot lowering accepts (f32 accumulate, narrowed
+    # once at the end, kernelization/lowering/dot.zig:2004-2015); here it runs on tcgen05
+    "plain": ([tensor.spec("f16", m=256, k=192), tensor.spec("f16", k=192, n=384)], lambda b, a: a[0].contract(a[1], "k")),
+    "bias_tanh": ([tensor.spec("f16", m=128, k=256), tensor.spec("f16", k=256, n=256), tensor.spec("f16", n=256)],
+                  lambda b, a: a[0].contract(a[1], "k").add(a[2]).tanh()),
+    "batched_k_major_b": ([tensor.spec("f16", g=3, m=128, k=128), tensor.spec("f16", g=3, n=128, k=128)],
+                          lambda b, a: a[0].contract(a[1], "k")),
+}
+
+
+@pytest.mark.parametrize("name", sorted(F16_PROGRAMS))
+def test_f16_matmul_on_tensor_cores(gpu_session, name):
+    specs, body = F16_PROGRAMS[name]
+    program = tensor.define("f16_" + name, specs, body)
+    rng = np.random.default_rng(11)
+    inputs = [(rng.standard_normal([e for _, e in sp.dims]) / 8.0).astype(np.float16) for sp in specs]
+    compiled = gpu_session.compile(program)
+    assert "tcgen05" in compiled.plan_summary()
+    out = np.empty(compiled.output_descriptors()[0].byte_size, np.uint8)
+    gpu_session.invoke(compiled, inputs, [out])
+    gpu_session.release(compiled)
+    want = oracle.run(program.wire, inputs, mode="wide")[0].astype(np.float64).reshape(-1)
+    got = out.view(np.float16).astype(np.float64)
+    rms = max(float(np.sqrt(np.mean(want * want))), 1e-30)
+    assert float(np.max(np.abs(got - want) / (np.abs(want) + rms))) < 2e-3   # f16 keeps 11 significant bits
+
+
 @pytest.mark.parametrize("seq,keys", [(256, 128), (512, 384), (256, 1152)])
 def test_cross_attention_key_lengths(gpu_session, seq, keys):
     """Non-causal attention whose key length differs from the query length: a single key block

@@ -2,7 +2,7 @@
 //
 // Replaces the reference's flash-attention lowering (src/preparation/kernelization/lowering/
 // flash.zig:330-604: f32 only, head dim 64, non-causal, 32x32 tiles of scalar FMAs) and its
-// library SDPA (src/kernel/library/attention.zig:389-441) with a tcgen05 kernel for bf16,
+// library SDPA (src/kernel/library/attention.zig:389-441) with a tcgen05 kernel for bf16 or f16,
 // head dim 128, optional causal mask, any number of leading batch axes:
 //   * a work item is 256 consecutive queries of one (batch, head), handled as two 128-row tiles;
 //     K/V blocks of 128 keys stream through a TMA ring and are shared by both tiles;
@@ -58,6 +58,8 @@ const char* kAttentionHead = R"CUDA(
 #define SCALE_LOG2 @SCALE_LOG2@f
 #define RESCALE_THRESHOLD 8.0f
 #define POLY_SHARE @POLY_SHARE@   // of every 8 pairs in the odd 32-column quarters
+#define AB_FORMAT @AB_FORMAT@   // operand format of the MMAs: 0 = f16, 1 = bf16 (P is written in the same format)
+#define PACK16 @PACK16@
 #define HALF_HANDOFF @HALF_HANDOFF@   // P is handed to the MMA issuer 64 keys at a time
 #ifndef INFINITY
 #define INFINITY __int_as_float(0x7f800000)
@@ -251,7 +253,7 @@ const char* kAttentionIssuer = R"CUDA(
     if (lane == 0) {
       const int t = warp == 1 ? 0 : 1;
       // S = Q K^T: A, B K-major, M = N = 128.  O += P V: A from TMEM, B = V with dim contiguous (N-major).
-      const unsigned int idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned int)(TILE >> 3) << 17) | ((unsigned int)(TILE >> 4) << 24);
+      const unsigned int idesc_s = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | ((unsigned int)(TILE >> 3) << 17) | ((unsigned int)(TILE >> 4) << 24);
       const unsigned int idesc_o = idesc_s | (1u << 16);
       const unsigned int s_tmem = tmem_base + t * TILE, o_tmem = tmem_base + 2 * TILE + t * TILE;
       const unsigned long long q_desc = smem_desc(smem_u32(q_smem + t * TILE_BYTES), 16, 1024);
@@ -469,7 +471,7 @@ const char* kAttentionSoftmax = R"CUDA(
             p1 = fast_exp2(p1);                                                              \
           }                                                                                  \
           ACC = add2(ACC, pk2(p0, p1));                                                      \
-          OUT[(AT) + (i >> 1)] = pack_bf16(p0, p1);                                          \
+          OUT[(AT) + (i >> 1)] = PACK16(p0, p1);                                          \
         }
         // The second half's arithmetic takes a word read after the arrival (always zero) as an
         // input, so that it cannot be scheduled ahead of the first half's store and arrival.
@@ -535,10 +537,10 @@ const char* kAttentionSoftmax = R"CUDA(
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const unsigned int* r = c < 4 ? ra + c * 8 : rb + (c - 4) * 8;
-          const uint4 v = make_uint4(pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv),
-                                     pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv),
-                                     pack_bf16(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv),
-                                     pack_bf16(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv));
+          const uint4 v = make_uint4(PACK16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv),
+                                     PACK16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv),
+                                     PACK16(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv),
+                                     PACK16(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv));
           *reinterpret_cast<uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) = v;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -597,6 +599,8 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
   const int poly_share = poly_code == 2 ? 2 : poly_code == 3 ? 4 : poly_code == 4 ? 8 : 0;
   replaceAll(src, "@POLY_SHARE@", std::to_string(poly_share));
   replaceAll(src, "@HALF_HANDOFF@", (ov.attention_poly & 8) ? "0" : "1");
+  replaceAll(src, "@AB_FORMAT@", a.dtype == DType::f16 ? "0u" : "1u");
+  replaceAll(src, "@PACK16@", a.dtype == DType::f16 ? "pack_f16" : "pack_bf16");
   KernelSource ks;
   ks.name = name;
   ks.family = "attention";

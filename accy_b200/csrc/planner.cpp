@@ -932,13 +932,20 @@ class Planner {
       case DType::f32: { float f; std::memcpy(&f, &bits, 4); *out = f; return true; }
       case DType::f64: { double d; std::memcpy(&d, &bits, 8); *out = d; return true; }
       case DType::bf16: { uint32_t w = static_cast<uint32_t>(bits & 0xffff) << 16; float f; std::memcpy(&f, &w, 4); *out = f; return true; }
+      case DType::f16: {
+        const uint32_t h = static_cast<uint32_t>(bits & 0xffff), sign = h >> 15, ex = (h >> 10) & 31, man = h & 1023;
+        double mag = ex == 0 ? std::ldexp(static_cast<double>(man), -24)
+                             : (ex == 31 ? (man ? std::nan("") : INFINITY) : std::ldexp(1.0 + man / 1024.0, static_cast<int>(ex) - 15));
+        *out = sign ? -mag : mag;
+        return true;
+      }
       default: return false;
     }
   }
 
   bool tryAttention(uint32_t v) {
     const Operation& pv = P.ops[v];
-    if (pv.result.dtype != DType::bf16) return false;
+    if (pv.result.dtype != DType::bf16 && pv.result.dtype != DType::f16) return false;
     DotShape s2;
     try { s2 = canonicalDot(pv); } catch (const PlanError&) { return false; }
     if (s2.nm != 1 || s2.nk != 1 || s2.nn != 1) return false;
@@ -1048,7 +1055,7 @@ class Planner {
     a.head_dim = g1.k;
     a.causal = causal;
     a.scale = static_cast<float>(scale);
-    a.dtype = DType::bf16;
+    a.dtype = pv.result.dtype;
     // layout requirements of the fused kernel: Q, K, V, O all [batch, seq, dim] row-major
     bool layout = g1.a_stride_k == 1 && g1.a_stride_m == a.head_dim && g1.b_stride_k == 1 &&
                   g1.b_stride_n == a.head_dim && g2.b_stride_n == 1 && g2.b_stride_k == g2.n &&

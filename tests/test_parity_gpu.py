@@ -139,6 +139,26 @@ def test_f16_matmul_on_tensor_cores(gpu_session, name):
     assert float(np.max(np.abs(got - want) / (np.abs(want) + rms))) < 2e-3   # f16 keeps 11 significant bits
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_f16_attention(gpu_session, causal):
+    """The fused attention kernel with f16 operands (P is written to TMEM as f16)."""
+    import math
+    specs = [tensor.spec("f16", batch=2, head=3, seq=512, dim=128), tensor.spec("f16", batch=2, head=3, key=512, dim=128),
+             tensor.spec("f16", batch=2, head=3, key=512, dim=128)]
+    program = tensor.define("attention_f16", specs, configs.make_attention_body(1.0 / math.sqrt(128), causal))
+    rng = np.random.default_rng(5)
+    inputs = [rng.standard_normal([e for _, e in sp.dims]).astype(np.float16) for sp in specs]
+    compiled = gpu_session.compile(program)
+    assert "attention:" in compiled.plan_summary()
+    out = np.empty(compiled.output_descriptors()[0].byte_size, np.uint8)
+    gpu_session.invoke(compiled, inputs, [out])
+    gpu_session.release(compiled)
+    want = oracle.run(program.wire, inputs, mode="wide")[0].astype(np.float64).reshape(-1)
+    got = out.view(np.float16).astype(np.float64)
+    rms = max(float(np.sqrt(np.mean(want * want))), 1e-30)
+    assert float(np.max(np.abs(got - want) / (np.abs(want) + rms))) < 4e-3
+
+
 @pytest.mark.parametrize("seq,keys", [(256, 128), (512, 384), (256, 1152)])
 def test_cross_attention_key_lengths(gpu_session, seq, keys):
     """Non-causal attention whose key length differs from the query length: a single key block

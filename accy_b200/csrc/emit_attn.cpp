@@ -3,7 +3,7 @@
 // Replaces the reference's flash-attention lowering (src/preparation/kernelization/lowering/
 // flash.zig:330-604: f32 only, head dim 64, non-causal, 32x32 tiles of scalar FMAs) and its
 // library SDPA (src/kernel/library/attention.zig:389-441) with a tcgen05 kernel for bf16 or f16,
-// head dim 128, optional causal mask, any number of leading batch axes:
+// head dim 128 or 64, optional causal mask, any number of leading batch axes:
 //   * a work item is 256 consecutive queries of one (batch, head), handled as two 128-row tiles;
 //     K/V blocks of 128 keys stream through a TMA ring and are shared by both tiles;
 //   * the kernel is persistent: one CTA per SM takes work items from a counter in global memory
@@ -48,10 +48,10 @@ const char* kAttentionHead = R"CUDA(
 #define SEQ_K @SEQ_K@
 #define BATCH @BATCH@
 #define CAUSAL @CAUSAL@
-#define HEAD_DIM 128
+#define HEAD_DIM @HEAD_DIM@   // 64 or 128
 #define TILE 128
 #define KV_STAGES 2
-#define TILE_BYTES (TILE * HEAD_DIM * 2)   // one 128 x 128 bf16 tile: two 64-wide boxes of 16 KB
+#define TILE_BYTES (TILE * HEAD_DIM * 2)   // one tile of 128 rows: HEAD_DIM / 64 boxes of 64 dims (16 KB each)
 #define HALF_BYTES (TILE * 64 * 2)
 #define N_PAIRS (SEQ_Q / (2 * TILE))
 #define N_ITEMS (N_PAIRS * BATCH)
@@ -220,18 +220,18 @@ extern "C" __global__ void __launch_bounds__(384, 1)
             if (!mbar_wait(BAR(B_Q_EMPTY), (unsigned int)(it & 1) ^ 1u, abort_flag)) { ok = false; break; }
             mbar_expect_tx(BAR(B_Q_FULL), 2 * TILE_BYTES);
             for (int t = 0; t < 2; ++t)
-              for (int h = 0; h < 2; ++h)
+              for (int h = 0; h < HEAD_DIM / 64; ++h)
                 tma_load_3d(smem_u32(q_smem + t * TILE_BYTES + h * HALF_BYTES), &map_q, BAR(B_Q_FULL), h * 64, q_row0 + t * TILE, bh);
           }
           const unsigned int stage = g % KV_STAGES;
           const unsigned int ph = (g / KV_STAGES) & 1u;
           if (!mbar_wait(BAR(B_K_EMPTY + stage), ph ^ 1u, abort_flag)) { ok = false; break; }
           mbar_expect_tx(BAR(B_K_FULL + stage), TILE_BYTES);
-          for (int h = 0; h < 2; ++h)
+          for (int h = 0; h < HEAD_DIM / 64; ++h)
             tma_load_3d(smem_u32(k_smem + stage * TILE_BYTES + h * HALF_BYTES), &map_k, BAR(B_K_FULL + stage), h * 64, j * TILE, bh);
           if (!mbar_wait(BAR(B_V_EMPTY + stage), ph ^ 1u, abort_flag)) { ok = false; break; }
           mbar_expect_tx(BAR(B_V_FULL + stage), TILE_BYTES);
-          for (int h = 0; h < 2; ++h)
+          for (int h = 0; h < HEAD_DIM / 64; ++h)
             tma_load_3d(smem_u32(v_smem + stage * TILE_BYTES + h * HALF_BYTES), &map_v, BAR(B_V_FULL + stage), h * 64, j * TILE, bh);
         }
         if (!ok) break;
@@ -254,7 +254,9 @@ const char* kAttentionIssuer = R"CUDA(
       const int t = warp == 1 ? 0 : 1;
       // S = Q K^T: A, B K-major, M = N = 128.  O += P V: A from TMEM, B = V with dim contiguous (N-major).
       const unsigned int idesc_s = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | ((unsigned int)(TILE >> 3) << 17) | ((unsigned int)(TILE >> 4) << 24);
-      const unsigned int idesc_o = idesc_s | (1u << 16);
+      // O += P V: M = 128, N = HEAD_DIM, B (= V) with the dims contiguous (N-major)
+      const unsigned int idesc_o = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | (1u << 16) |
+                                   ((unsigned int)(HEAD_DIM >> 3) << 17) | ((unsigned int)(TILE >> 4) << 24);
       const unsigned int s_tmem = tmem_base + t * TILE, o_tmem = tmem_base + 2 * TILE + t * TILE;
       const unsigned long long q_desc = smem_desc(smem_u32(q_smem + t * TILE_BYTES), 16, 1024);
       auto wait_turn = [&](unsigned int want) {
@@ -433,7 +435,7 @@ const char* kAttentionSoftmax = R"CUDA(
             tc_fence_after();
             // rare path: the first score registers serve as scratch and the scores are read again
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < HEAD_DIM / 32; ++c) {
               tc_ld32(o_addr + c * 32, r0);
               tc_wait_ld();
 #pragma unroll
@@ -527,7 +529,7 @@ const char* kAttentionSoftmax = R"CUDA(
       // benchmark 6 % (14 % for 1024-key items).
       unsigned char* stage = o_stage + (warp - 2) * 4096;
 #pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
+      for (int half = 0; half < HEAD_DIM / 64; ++half) {
         unsigned int ra[32], rb[32];
         tc_ld32(o_addr + half * 64, ra);
         tc_ld32(o_addr + half * 64 + 32, rb);
@@ -579,13 +581,14 @@ const char* kAttentionTail = R"CUDA(
 }  // namespace
 
 void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, const ScheduleOverrides& ov) {
-  if (a.head_dim != 128 || a.q_len % 256 != 0 || a.k_len % 128 != 0)
+  if ((a.head_dim != 128 && a.head_dim != 64) || a.q_len % 256 != 0 || a.k_len % 128 != 0)
     throw PlanError("attention shape not covered by the fused kernel");
   std::string src = std::string(kConvertPrelude) + kTcPreludeShared + kAttentionHead + kAttentionIssuer + kAttentionSoftmax + kAttentionTail;
   std::ostringstream scale;
   scale.precision(9);
   scale << std::scientific << static_cast<double>(a.scale) * 1.4426950408889634;
   replaceAll(src, "@KERNEL@", name);
+  replaceAll(src, "@HEAD_DIM@", std::to_string(a.head_dim));
   replaceAll(src, "@SEQ_Q@", std::to_string(a.q_len));
   replaceAll(src, "@SEQ_K@", std::to_string(a.k_len));
   replaceAll(src, "@BATCH@", std::to_string(a.batch));
@@ -624,11 +627,11 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
     m.tma.rank = 3;
     m.tma.elem_bytes = 2;
     m.tma.swizzle = 3;
-    m.tma.dims[0] = 128;
+    m.tma.dims[0] = static_cast<uint64_t>(a.head_dim);
     m.tma.dims[1] = static_cast<uint64_t>(seq);
     m.tma.dims[2] = static_cast<uint64_t>(a.batch);
-    m.tma.strides[0] = 128 * 2;
-    m.tma.strides[1] = static_cast<uint64_t>(seq) * 128 * 2;
+    m.tma.strides[0] = static_cast<uint64_t>(a.head_dim) * 2;
+    m.tma.strides[1] = static_cast<uint64_t>(seq) * a.head_dim * 2;
     m.tma.box[0] = 64;
     m.tma.box[1] = 128;
     m.tma.box[2] = 1;

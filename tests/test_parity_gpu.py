@@ -101,7 +101,9 @@ def test_dot_f32_known_answer(gpu_session):
                                                         (1, 2, 256, 128, False), (1, 3, 1024, 128, True),
                                                         (2, 1, 512, 128, False), (1, 1, 2048, 128, True),
                                                         # more work items than SMs: CTAs take several items each
-                                                        (4, 10, 1024, 128, True), (3, 26, 512, 128, False)])
+                                                        (4, 10, 1024, 128, True), (3, 26, 512, 128, False),
+                                                        # head dim 64 in the fused kernel
+                                                        (2, 2, 512, 64, True), (1, 3, 256, 64, False), (2, 40, 512, 64, True)])
 def test_attention_matches_f32_reference(gpu_session, batch, head, seq, dim, causal):
     cfg = configs.attention(batch, head, seq, dim, causal)
     inputs = cfg.make_inputs()

@@ -151,7 +151,7 @@ struct ScheduleOverrides {
   int column_splits = 0;
   int force_simt_gemm = 0;
   int row_min_blocks = 0;
-  int attention_poly = 0;        // 0 automatic, 1 none, 2 = 1/8, 3 = 1/4, 4 = 1/2 of the exponentials by polynomial
+  int attention_poly = 0;        // low 3 bits: 0 automatic, 1 none, 2 = 1/8, 3 = 1/4, 4 = 1/2 of the exponentials by polynomial; +8: P handed over in one piece
   int sm_count = 148;
 };
 

@@ -63,8 +63,9 @@ typedef struct accy_b200_options {
   int32_t force_simt_gemm;    /* 1 = never use the tcgen05 kernels (exact k-serial order) */
   int32_t row_min_blocks;     /* schedule override: resident CTAs per SM requested of row kernels, 0 = automatic */
   int32_t single_shot_invoke; /* 1 = host-buffer invoke never streams the program through the GPU in chunks */
-  int32_t attention_poly;     /* attention: share of exponentials computed by polynomial on the FMA pipe instead of
-                                 the special-function unit. 0 = automatic, 1 = none, 2 = 1/8, 3 = 1/4, 4 = 1/2 */
+  int32_t attention_poly;     /* attention schedule (experiments): low three bits = share of exponentials computed by
+                                 polynomial on the FMA pipe instead of the special-function unit (0 = automatic, 1 = none,
+                                 2 = 1/8, 3 = 1/4, 4 = 1/2); +8 = hand P to the MMA issuer in one piece, not two halves */
 } accy_b200_options;
 
 /* One input or output slot: session.zig:66-74 (Descriptor). */

@@ -216,11 +216,37 @@ std::string driverErrorName(CUresult_t r) {
   return s ? std::string(s) : ("CUresult " + std::to_string(r));
 }
 
+// Compiled kernels are kept for the life of the process, keyed by the exact source text and
+// options (the reference keeps its JIT-compiled modules keyed by PTX text,
+// deps/lib/compiler/gpu/src/cuda.zig): compiling a program a second time, in this or another
+// session, costs a lookup instead of 0.3-1.4 s of NVRTC per kernel.  ACCY_B200_NO_KERNEL_CACHE=1
+// turns it off.
+namespace {
+std::mutex g_cubin_mutex;
+std::map<std::string, std::vector<char>> g_cubins;
+size_t g_cubin_bytes = 0;
+constexpr size_t kCubinCacheLimit = 256u << 20;
+}  // namespace
+
 std::vector<char> compileToCubin(const std::string& source, const std::string& name,
                                  const std::vector<std::string>& extra_options, std::string* log) {
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     if (!g_nvrtc.loaded) loadNvrtc();
+  }
+  const char* no_cache = getenv("ACCY_B200_NO_KERNEL_CACHE");
+  const bool cached = !(no_cache && *no_cache == '1');
+  std::string key;
+  if (cached) {
+    for (const std::string& o : extra_options) key += o + '\n';
+    key += '\0';
+    key += source;
+    std::lock_guard<std::mutex> lock(g_cubin_mutex);
+    auto hit = g_cubins.find(key);
+    if (hit != g_cubins.end()) {
+      if (log) log->clear();
+      return hit->second;
+    }
   }
   void* prog = nullptr;
   int rc = g_nvrtc.createProgram(&prog, source.c_str(), (name + ".cu").c_str(), 0, nullptr, nullptr);
@@ -244,6 +270,11 @@ std::vector<char> compileToCubin(const std::string& source, const std::string& n
   std::vector<char> cubin(size);
   g_nvrtc.getCUBIN(prog, cubin.data());
   g_nvrtc.destroyProgram(&prog);
+  if (cached) {
+    std::lock_guard<std::mutex> lock(g_cubin_mutex);
+    if (g_cubin_bytes + cubin.size() + key.size() <= kCubinCacheLimit && g_cubins.emplace(key, cubin).second)
+      g_cubin_bytes += cubin.size() + key.size();
+  }
   return cubin;
 }
 

@@ -368,6 +368,21 @@ def test_resident_inputs_are_copied_once(fake_driver):
     session.deinit()
 
 
+def test_compiled_kernels_are_reused_across_sessions():
+    """A program compiled a second time (another session, same process) takes its kernels from the
+    process-wide cache keyed by source text: the kernel_compile phase all but disappears."""
+    program = configs.mismatch(7, 4099).program()   # extents no other test uses
+    spent = []
+    for _ in range(2):
+        session = tensor.Session(device=-1)
+        phases = {}
+        session.set_observer(lambda phase, ns: phases.__setitem__(phase, phases.get(phase, 0) + ns))
+        session.compile(program)
+        spent.append(phases["kernel_compile"])
+        session.deinit()
+    assert spent[1] * 5 < spent[0]
+
+
 def test_failed_launch_poisons_the_session(fake_driver):
     session = tensor.Session(device=0)
     cfg = configs.mismatch(8, 16)

@@ -19,7 +19,9 @@
 //     tensor cores serve the other tile;
 //   * online softmax in f32 in the log2 domain (ex2.approx of fma(s, scale*log2e, -m)); O is only
 //     rescaled when a row's running max grows by more than 2^8, so the rescale through TMEM is rare;
-//   * causal programs skip key blocks above the diagonal and mask only the diagonal block.
+//   * causal programs skip key blocks above the diagonal and mask only the diagonal block;
+//   * lengths need not be multiples of the tiles: loads past the end read zeros, the last key
+//     block is masked, stores past the end are dropped.
 // Every wait is bounded; on expiry the kernel sets the device status word and returns.
 #include <algorithm>
 #include <cmath>
@@ -53,7 +55,8 @@ const char* kAttentionHead = R"CUDA(
 #define KV_STAGES 2
 #define TILE_BYTES (TILE * HEAD_DIM * 2)   // one tile of 128 rows: HEAD_DIM / 64 boxes of 64 dims (16 KB each)
 #define HALF_BYTES (TILE * 64 * 2)
-#define N_PAIRS (SEQ_Q / (2 * TILE))
+#define N_PAIRS ((SEQ_Q + 2 * TILE - 1) / (2 * TILE))   // lengths need not be multiples of the tile: TMA
+                                                        // loads read zeros past the end, TMA stores drop such rows
 #define N_ITEMS (N_PAIRS * BATCH)
 #define SCALE_LOG2 @SCALE_LOG2@f
 #define RESCALE_THRESHOLD 8.0f
@@ -129,7 +132,7 @@ __device__ __forceinline__ void decode_item(int item, int& bh, int& q_row0, int&
   n0 = q_row0 / TILE + 1;
   n1 = n0 + 1;
 #else
-  n0 = SEQ_K / TILE;
+  n0 = (SEQ_K + TILE - 1) / TILE;
   n1 = n0;
 #endif
 }
@@ -389,7 +392,11 @@ const char* kAttentionSoftmax = R"CUDA(
       for (int j = 0; ok && j < n_t; ++j, ++done) {
         if (!mbar_wait(BAR(B_S_FULL + t), done & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const bool diagonal = CAUSAL && (j == n_t - 1);
+        // The last key block is masked: on the diagonal (causal) a row sees the keys up to its own
+        // index, which also hides keys past the end; without a causal mask only a ragged key
+        // length needs it, and every row sees the same SEQ_K % TILE keys of that block.
+        const bool diagonal = (CAUSAL || SEQ_K % TILE != 0) && (j == n_t - 1);
+        const int lim = CAUSAL ? row : SEQ_K % TILE - 1;
         // the whole score row (128 columns) is read once and stays in registers for the row max
         // and for the exponentials; the four loads are in flight together
         unsigned int r0[32], r1[32], r2[32], r3[32];
@@ -406,10 +413,10 @@ const char* kAttentionSoftmax = R"CUDA(
           if (diagonal) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              a = fmaxf(a, i > row ? -INFINITY : __uint_as_float(r0[i]));
-              b = fmaxf(b, 32 + i > row ? -INFINITY : __uint_as_float(r1[i]));
-              c = fmaxf(c, 64 + i > row ? -INFINITY : __uint_as_float(r2[i]));
-              d = fmaxf(d, 96 + i > row ? -INFINITY : __uint_as_float(r3[i]));
+              a = fmaxf(a, i > lim ? -INFINITY : __uint_as_float(r0[i]));
+              b = fmaxf(b, 32 + i > lim ? -INFINITY : __uint_as_float(r1[i]));
+              c = fmaxf(c, 64 + i > lim ? -INFINITY : __uint_as_float(r2[i]));
+              d = fmaxf(d, 96 + i > lim ? -INFINITY : __uint_as_float(r3[i]));
             }
           } else {
 #pragma unroll
@@ -466,8 +473,8 @@ const char* kAttentionSoftmax = R"CUDA(
           } else {                                                                           \
             upk2(x2, p0, p1);                                                                \
             if (MASKED) {                                                                    \
-              if ((COL0) + i > row) p0 = -INFINITY;                                          \
-              if ((COL0) + i + 1 > row) p1 = -INFINITY;                                      \
+              if ((COL0) + i > lim) p0 = -INFINITY;                                          \
+              if ((COL0) + i + 1 > lim) p1 = -INFINITY;                                      \
             }                                                                                \
             p0 = fast_exp2(p0);                                                              \
             p1 = fast_exp2(p1);                                                              \
@@ -581,7 +588,7 @@ const char* kAttentionTail = R"CUDA(
 }  // namespace
 
 void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, const ScheduleOverrides& ov) {
-  if ((a.head_dim != 128 && a.head_dim != 64) || a.q_len % 256 != 0 || a.k_len % 128 != 0)
+  if ((a.head_dim != 128 && a.head_dim != 64) || a.q_len < 128 || a.k_len < 128)
     throw PlanError("attention shape not covered by the fused kernel");
   std::string src = std::string(kConvertPrelude) + kTcPreludeShared + kAttentionHead + kAttentionIssuer + kAttentionSoftmax + kAttentionTail;
   std::ostringstream scale;
@@ -612,7 +619,7 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
 
   Launch l;
   l.kernel = static_cast<int>(plan.kernels.size()) - 1;
-  const long long items = (a.q_len / 256) * a.batch;
+  const long long items = ((a.q_len + 255) / 256) * a.batch;
   if (items > 0x7fffffffll) throw PlanError("too many attention work items");
   // persistent: one CTA per SM (the kernel's shared memory allows one), fewer when there is less work
   l.grid[0] = static_cast<uint32_t>(std::min<long long>(items, ov.sm_count));

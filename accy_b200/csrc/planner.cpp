@@ -1062,7 +1062,7 @@ class Planner {
                   g2.n == a.head_dim && g2.k == a.k_len &&
                   (a.batch == 1 || (g1.a_stride_b == a.q_len * a.head_dim && g1.b_stride_b == a.k_len * a.head_dim &&
                                     g2.b_stride_b == a.k_len * a.head_dim));
-    bool shape = (a.head_dim == 128 || a.head_dim == 64) && a.q_len % 256 == 0 && a.k_len % 128 == 0 && (!causal || a.q_len == a.k_len) &&
+    bool shape = (a.head_dim == 128 || a.head_dim == 64) && a.q_len >= 128 && a.k_len >= 128 && (!causal || a.q_len == a.k_len) &&
                  scale > 0.0;
     if (!layout || !shape || ov.force_simt_gemm || !attentionReady()) return false;
     a.q_slot = g1.a_slot;

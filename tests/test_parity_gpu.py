@@ -161,6 +161,26 @@ def test_f16_attention(gpu_session, causal):
     assert float(np.max(np.abs(got - want) / (np.abs(want) + rms))) < 4e-3
 
 
+@pytest.mark.parametrize("seq,keys,dim,causal", [(1000, 1000, 128, True), (700, 700, 64, True), (600, 600, 128, True),
+                                                  (384, 200, 128, False), (300, 300, 64, False), (129, 129, 128, True)])
+def test_ragged_attention_lengths(gpu_session, seq, keys, dim, causal):
+    """Sequence lengths that are not multiples of the 128-row tile still run in the fused kernel:
+    loads past the end read zeros, the last key block is masked, stores past the end are dropped."""
+    cfg = configs.attention(2, 3, seq, dim, causal, keys=keys)
+    inputs = cfg.make_inputs()
+    program = cfg.program()
+    compiled = gpu_session.compile(program)
+    assert "attention:" in compiled.plan_summary()
+    guard = 0x5A
+    out = np.full(compiled.output_descriptors()[0].byte_size + 4096, guard, np.uint8)
+    gpu_session.invoke(compiled, inputs, [out[:-4096]])
+    gpu_session.release(compiled)
+    assert np.all(out[-4096:] == guard)
+    got = configs.bf16_bits_to_f32(out[:-4096].view(np.uint16))
+    ref = configs.bf16_bits_to_f32(oracle.run(program.wire, inputs, mode="wide")[0]).reshape(-1)
+    assert rel_err_bf16(got, ref) < 2e-2
+
+
 @pytest.mark.parametrize("seq,keys", [(256, 128), (512, 384), (256, 1152)])
 def test_cross_attention_key_lengths(gpu_session, seq, keys):
     """Non-causal attention whose key length differs from the query length: a single key block

@@ -130,6 +130,7 @@ const char* kGemmTemplate = R"CUDA(
 #define BLOCK_N @BLOCK_N@
 #define AB_FORMAT @AB_FORMAT@
 #define BLOCK_K 64
+#define VECTOR_STORES @VECTOR_STORES@   // rows of C start 16-byte aligned
 #define STAGES @STAGES@
 #define M_TOTAL @M@ll
 #define N_TOTAL @N@ll
@@ -170,7 +171,10 @@ extern "C" __global__ void __launch_bounds__(192, 1)
   tc_fence_after();
   const unsigned int tmem_base = *tmem_holder;
 
-  const long long m_blocks = M_TOTAL / BLOCK_M, n_blocks = N_TOTAL / BLOCK_N, k_blocks = K_TOTAL / BLOCK_K;
+  // extents need not be multiples of the tile: TMA loads read zeros past the end (zeros add nothing
+  // to the sums), the epilogue clamps the indices it reads operands at and stores only inside
+  const long long m_blocks = (M_TOTAL + BLOCK_M - 1) / BLOCK_M, n_blocks = (N_TOTAL + BLOCK_N - 1) / BLOCK_N,
+                  k_blocks = (K_TOTAL + BLOCK_K - 1) / BLOCK_K;
   const long long tiles_per_batch = m_blocks * n_blocks;
   const long long num_tiles = tiles_per_batch * BATCH;
 
@@ -273,7 +277,9 @@ extern "C" __global__ void __launch_bounds__(192, 1)
       tile_coords(tile, bi, mb, nb);
       if (!mbar_wait(tfull0 + 8 * buf, acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const long long mi = mb * BLOCK_M + row_in_tile;
+      const long long mi_raw = mb * BLOCK_M + row_in_tile;
+      const bool row_inside = mi_raw < M_TOTAL;
+      const long long mi = row_inside ? mi_raw : M_TOTAL - 1;
       @OUT_T@* crow = C + (bi * M_TOTAL + mi) * N_TOTAL + nb * BLOCK_N;
       const unsigned int taddr = tmem_base + ((quarter * 32u) << 16) + buf * BLOCK_N;
 #pragma unroll 1
@@ -285,12 +291,21 @@ extern "C" __global__ void __launch_bounds__(192, 1)
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const float acc = __uint_as_float(r[j]);
-          const long long ni = nb * BLOCK_N + c * 32 + j;
+          const long long ni_raw = nb * BLOCK_N + c * 32 + j;
+          const long long ni = (N_TOTAL % BLOCK_N == 0 || ni_raw < N_TOTAL) ? ni_raw : N_TOTAL - 1;
           (void)ni;
 @EPI_BODY@
           v[j] = @EPI_RESULT@;
         }
+        const long long n_left = N_TOTAL - (nb * BLOCK_N + c * 32);   // columns of this chunk inside the matrix
+        if (row_inside && n_left >= 32 && VECTOR_STORES) {
 @STORE@
+        } else if (row_inside && n_left > 0) {
+          const int count = n_left < 32 ? (int)n_left : 32;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < count) crow[c * 32 + j] = @SCALAR_STORE@;
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -348,6 +363,9 @@ void emitGemmTcgen05(const GemmOp& g, const std::string& name, Plan& plan, const
 
   std::string src = std::string(kConvertPrelude) + kTcPrelude + kGemmTemplate;
   if (g.out_dtype == DType::f16) replaceAll(store, "pack_bf16(", "pack_f16(");
+  const int out_bytes = g.out_dtype == DType::f32 ? 4 : 2;
+  replaceAll(src, "@VECTOR_STORES@", (g.n * out_bytes) % 16 == 0 ? "1" : "0");
+  replaceAll(src, "@SCALAR_STORE@", g.out_dtype == DType::f32 ? "v[j]" : (g.out_dtype == DType::f16 ? "f32_to_f16(v[j])" : "f32_to_bf16(v[j])"));
   replaceAll(src, "@KERNEL@", name);
   replaceAll(src, "@AB_FORMAT@", g.in_dtype == DType::f16 ? "0u" : "1u");
   replaceAll(src, "@BLOCK_N@", std::to_string(block_n));
@@ -372,7 +390,7 @@ void emitGemmTcgen05(const GemmOp& g, const std::string& name, Plan& plan, const
 
   Launch l;
   l.kernel = static_cast<int>(plan.kernels.size()) - 1;
-  const long long tiles = (g.m / 128) * (g.n / block_n) * g.batch;
+  const long long tiles = ((g.m + 127) / 128) * ((g.n + block_n - 1) / block_n) * g.batch;
   l.grid[0] = static_cast<uint32_t>(std::min<long long>(tiles, ov.sm_count));
   l.block[0] = 192;
   const uint32_t stage_bytes = 128 * 64 * 2 + block_n * 64 * 2;

@@ -827,8 +827,10 @@ class Planner {
     }
     g.c_slot = destinationSlot(root);
     g.out_dtype = plan.slots[g.c_slot].storage;
-    const bool aligned = g.m % 128 == 0 && g.n % 128 == 0 && g.k % 64 == 0 && g.a_stride_k == 1 &&
-                         (g.b_stride_n == 1 || g.b_stride_k == 1);
+    // the tensor-core kernel takes ragged extents (TMA zero fill, guarded stores); what it needs
+    // is at least one full tile per dimension and 16-byte row strides for the TMA descriptors
+    const bool aligned = g.m >= 128 && g.n >= 128 && g.k >= 64 && g.k % 8 == 0 && g.a_stride_k == 1 &&
+                         ((g.b_stride_n == 1 && g.n % 8 == 0) || g.b_stride_k == 1);
     const bool half_inputs = (g.in_dtype == DType::bf16 && g.b_dtype == DType::bf16) || (g.in_dtype == DType::f16 && g.b_dtype == DType::f16);
     g.tensor_core = half_inputs && aligned && !ov.force_simt_gemm && tcgen05Ready();
     std::string name = nextName(g.tensor_core ? "gemm_tc" : "gemm_simt");

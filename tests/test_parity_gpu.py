@@ -113,6 +113,37 @@ def test_attention_matches_f32_reference(gpu_session, batch, head, seq, dim, cau
     assert rel_err_bf16(got, ref) < 2e-2
 
 
+RAGGED_GEMMS = {
+    "ragged_all": ([tensor.spec("bf16", m=300, k=200), tensor.spec("bf16", k=200, n=392)], lambda b, a: a[0].contract(a[1], "k")),
+    "ragged_bias_tanh": ([tensor.spec("bf16", m=1000, k=72), tensor.spec("bf16", k=72, n=1032), tensor.spec("bf16", n=1032)],
+                         lambda b, a: a[0].contract(a[1], "k").add(a[2]).tanh()),
+    "one_tile_plus_a_bit": ([tensor.spec("bf16", m=129, k=64), tensor.spec("bf16", k=64, n=136)], lambda b, a: a[0].contract(a[1], "k")),
+    "batched_k_major_b": ([tensor.spec("bf16", g=3, m=200, k=136), tensor.spec("bf16", g=3, n=150, k=136)],
+                          lambda b, a: a[0].contract(a[1], "k")),
+    "f32_output_odd_n": ([tensor.spec("bf16", m=130, k=128), tensor.spec("bf16", n=131, k=128)], lambda b, a: a[0].contract(a[1], "k")),
+}
+
+
+@pytest.mark.parametrize("name", sorted(RAGGED_GEMMS))
+def test_ragged_matmul_on_tensor_cores(gpu_session, name):
+    """Extents that are not multiples of the 128 x 128/256 x 64 tile stay on tcgen05: loads past
+    the end read zeros, stores are guarded (bytes after the output stay untouched)."""
+    specs, body = RAGGED_GEMMS[name]
+    program = tensor.define("gemm_" + name, specs, body)
+    rng = np.random.default_rng(13)
+    inputs = [configs.f32_to_bf16_bits((rng.standard_normal([e for _, e in sp.dims]) / 8.0).astype(np.float32)) for sp in specs]
+    compiled = gpu_session.compile(program)
+    assert "tcgen05" in compiled.plan_summary()
+    size = compiled.output_descriptors()[0].byte_size
+    out = np.full(size + 4096, 0x5A, np.uint8)
+    gpu_session.invoke(compiled, inputs, [out[:size]])
+    gpu_session.release(compiled)
+    assert np.all(out[size:] == 0x5A)
+    got = configs.bf16_bits_to_f32(out[:size].view(np.uint16))
+    ref = configs.bf16_bits_to_f32(oracle.run(program.wire, inputs, mode="wide")[0]).reshape(-1)
+    assert rel_err_bf16(got, ref) < 2e-2
+
+
 F16_PROGRAMS = {
     # f16 is the 16-bit float the reference's own dot lowering accepts (f32 accumulate, narrowed
     # once at the end, kernelization/lowering/dot.zig:2004-2015); here it runs on tcgen05

@@ -6,6 +6,7 @@
 // k folded serially as acc = acc + a*b with separate multiply and add roundings (compiled with
 // --fmad=false), 16-bit inputs widened to f32 and narrowed once at the end (:2004-2015).  It is
 // the exact-order path used for f32 programs and for shapes the tensor-core tiles do not cover.
+#include <cstdlib>
 #include <sstream>
 
 #include "plan.hpp"
@@ -128,9 +129,128 @@ static void emitGemmSimt(const GemmOp& g, const std::string& name, Plan& plan) {
   plan.launches.push_back(l);
 }
 
+// The same arithmetic as emitGemmSimt (every output folds k serially, acc = acc + a*b with separate
+// multiply and add roundings, so the results are bit-identical to it) laid out as a classic
+// shared-memory SGEMM: 128 x 128 output tile per CTA of 256 threads, 16-deep k slices staged in
+// shared memory (two buffers), 8 x 8 outputs per thread in two 4-wide groups 64 apart so that the
+// 128-bit shared-memory reads are conflict free.  Any strides,
+// any extents (guards instead of padding: a zero added past the end could turn a -0 sum into +0).
+static void emitGemmSimtTiled(const GemmOp& g, const std::string& name, Plan& plan) {
+  std::ostringstream o;
+  const std::string in_t = storageTypeOf(g.in_dtype), b_t = storageTypeOf(g.b_dtype), out_t = storageTypeOf(g.out_dtype);
+  const long long m_blocks = (g.m + 127) / 128, n_blocks = (g.n + 127) / 128;
+  o << kConvertPrelude;
+  o << "#define GM " << g.m << "ll\n#define GN " << g.n << "ll\n#define GK " << g.k << "ll\n";
+  o << "#define A_SB " << g.a_stride_b << "ll\n#define A_SM " << g.a_stride_m << "ll\n#define A_SK " << g.a_stride_k << "ll\n";
+  o << "#define B_SB " << g.b_stride_b << "ll\n#define B_SK " << g.b_stride_k << "ll\n#define B_SN " << g.b_stride_n << "ll\n";
+  o << "#define M_BLOCKS " << m_blocks << "ll\n#define N_BLOCKS " << n_blocks << "ll\n";
+  o << "#define LOAD_A(p) " << loadConv(g.in_dtype, "(p)") << "\n#define LOAD_B(p) " << loadConv(g.b_dtype, "(p)") << "\n";
+  o << "extern \"C\" __global__ void __launch_bounds__(256, 2) " << name << "(const " << in_t << "* __restrict__ A, const "
+    << b_t << "* __restrict__ B, " << out_t << "* __restrict__ C" << epilogueParams(g.epilogue) << ") {\n";
+  o << R"CUDA(
+  __shared__ __align__(16) float As[2][16][128];
+  __shared__ __align__(16) float Bs[2][16][128];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const long long tile = blockIdx.x;
+  const long long nb = tile % N_BLOCKS, mb = (tile / N_BLOCKS) % M_BLOCKS, bi = tile / (N_BLOCKS * M_BLOCKS);
+  const long long m0 = mb * 128, n0 = nb * 128;
+  const long long a_base = bi * A_SB, b_base = bi * B_SB;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+  // one k slice: 128 x 16 of A and 16 x 128 of B, eight elements of each per thread; the thread
+  // order follows whichever index is contiguous in memory
+  auto load_slice = [&](int buf, long long k0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = tid + i * 256;
+      const int mm = A_SK == 1 ? e >> 4 : e & 127, kk = A_SK == 1 ? e & 15 : e >> 7;
+      const long long gm = m0 + mm, gk = k0 + kk;
+      As[buf][kk][mm] = (gm < GM && gk < GK) ? LOAD_A(A[a_base + gm * A_SM + gk * A_SK]) : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = tid + i * 256;
+      const int nn = B_SN == 1 ? e & 127 : e >> 4, kk = B_SN == 1 ? e >> 7 : e & 15;
+      const long long gn = n0 + nn, gk = k0 + kk;
+      Bs[buf][kk][nn] = (gn < GN && gk < GK) ? LOAD_B(B[b_base + gk * B_SK + gn * B_SN]) : 0.0f;
+    }
+  };
+  auto step = [&](int buf, int kk) {
+    const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
+    const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
+    const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
+    const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
+    const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float prod = a[i] * b[j];   // compiled without contraction: two roundings, as the reference
+        acc[i][j] = acc[i][j] + prod;
+      }
+  };
+  const long long slices = (GK + 15) / 16;
+  load_slice(0, 0);
+  __syncthreads();
+  for (long long s = 0; s < slices; ++s) {
+    const int buf = (int)(s & 1);
+    if (s + 1 < slices) load_slice(buf ^ 1, (s + 1) * 16);
+    const long long left = GK - s * 16;
+    if (left >= 16) {
+#pragma unroll
+      for (int kk = 0; kk < 16; ++kk) step(buf, kk);
+    } else {
+      for (int kk = 0; kk < (int)left; ++kk) step(buf, kk);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const long long mi = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const long long ni = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+      const float acc_v = acc[i][j];
+      if (mi < GM && ni < GN) {
+)CUDA";
+  std::string result = emitEpilogueBody(g.epilogue, o, "        ", "acc_v", "bi", "mi", "ni", "");
+  o << "        C[(bi * GM + mi) * GN + ni] = " << storeConv(g.out_dtype, result) << ";\n";
+  o << "      }\n    }\n  }\n}\n";
+  KernelSource ks;
+  ks.name = name;
+  ks.family = "gemm_simt";
+  ks.source = o.str();
+  ks.options.push_back("--fmad=false");
+  plan.kernels.push_back(ks);
+  Launch l;
+  l.kernel = static_cast<int>(plan.kernels.size()) - 1;
+  const long long tiles = m_blocks * n_blocks * g.batch;
+  if (tiles > 0x7fffffffll) throw PlanError("dot_general output too large for the SIMT kernel");
+  l.grid[0] = static_cast<uint32_t>(tiles);
+  l.block[0] = 256;
+  l.label = name;
+  KernelArg a;
+  a.slot = g.a_slot;
+  l.args.push_back(a);
+  a.slot = g.b_slot;
+  l.args.push_back(a);
+  a.slot = g.c_slot;
+  l.args.push_back(a);
+  for (const LeafRef& leaf : g.epilogue.leaves) {
+    a.slot = leaf.slot;
+    l.args.push_back(a);
+  }
+  plan.launches.push_back(l);
+}
+
 void emitGemm(const GemmOp& g, const std::string& name, Plan& plan, const ScheduleOverrides& o) {
   if (g.in_dtype == DType::f64) throw PlanError("f64 dot_general is not supported");
   if (g.tensor_core) emitGemmTcgen05(g, name, plan, o);
+  else if (g.batch * g.m * g.n >= 4096 && g.k >= 8) emitGemmSimtTiled(g, name, plan);   // tiny ones: one thread per output
   else emitGemmSimt(g, name, plan);
 }
 

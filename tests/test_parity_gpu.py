@@ -113,6 +113,34 @@ def test_attention_matches_f32_reference(gpu_session, batch, head, seq, dim, cau
     assert rel_err_bf16(got, ref) < 2e-2
 
 
+F32_GEMMS = {
+    "ragged_bias": ([tensor.spec("f32", m=1000, k=333), tensor.spec("f32", k=333, n=517), tensor.spec("f32", n=517)],
+                    lambda b, a: a[0].contract(a[1], "k").add(a[2])),
+    "batched_k_major_b": ([tensor.spec("f32", g=3, m=130, k=77), tensor.spec("f32", g=3, n=200, k=77)], lambda b, a: a[0].contract(a[1], "k")),
+    "m_contiguous_a": ([tensor.spec("f32", k=96, m=256), tensor.spec("f32", k=96, n=128)], lambda b, a: a[0].contract(a[1], "k")),
+    "small": ([tensor.spec("f32", m=50, k=30), tensor.spec("f32", k=30, n=70)], lambda b, a: a[0].contract(a[1], "k")),
+    "short_k": ([tensor.spec("f32", m=256, k=5), tensor.spec("f32", k=5, n=256)], lambda b, a: a[0].contract(a[1], "k")),
+}
+
+
+@pytest.mark.parametrize("name", sorted(F32_GEMMS))
+def test_f32_matmul_is_bit_exact(gpu_session, name):
+    """f32 contractions keep the reference's arithmetic (k folded serially, separate multiply and
+    add roundings, dot.zig:2049-2115) in the tiled kernel too: the bits equal the oracle's."""
+    specs, body = F32_GEMMS[name]
+    program = tensor.define("gemm_f32_" + name, specs, body)
+    rng = np.random.default_rng(17)
+    inputs = [rng.standard_normal([e for _, e in sp.dims]).astype(np.float32) for sp in specs]
+    compiled = gpu_session.compile(program)
+    size = compiled.output_descriptors()[0].byte_size
+    out = np.full(size + 4096, 0x5A, np.uint8)
+    gpu_session.invoke(compiled, inputs, [out[:size]])
+    gpu_session.release(compiled)
+    assert np.all(out[size:] == 0x5A)
+    want = oracle.run(program.wire, inputs, mode="ref")[0].astype(np.float32).reshape(-1)
+    assert np.array_equal(out[:size].view(np.float32).view(np.uint32), want.view(np.uint32))
+
+
 RAGGED_GEMMS = {
     "ragged_all": ([tensor.spec("bf16", m=300, k=200), tensor.spec("bf16", k=200, n=392)], lambda b, a: a[0].contract(a[1], "k")),
     "ragged_bias_tanh": ([tensor.spec("bf16", m=1000, k=72), tensor.spec("bf16", k=72, n=1032), tensor.spec("bf16", n=1032)],

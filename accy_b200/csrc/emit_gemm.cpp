@@ -95,11 +95,15 @@ static void emitGemmSimt(const GemmOp& g, const std::string& name, Plan& plan) {
     << "ll;\n  const long long bi = idx / " << g.m * g.n << "ll;\n";
   o << "  const " << in_t << "* a = A + bi * " << g.a_stride_b << "ll + mi * " << g.a_stride_m << "ll;\n";
   o << "  const " << storageTypeOf(g.b_dtype) << "* b = B + bi * " << g.b_stride_b << "ll + ni * " << g.b_stride_n << "ll;\n";
-  o << "  float acc = 0.0f;\n";
+  // integers (the reference's dot lowering takes i32 and u32, dot.zig:2211-2233) wrap around:
+  // the arithmetic is done on unsigned values, whose overflow is defined
+  const bool integer = g.in_dtype == DType::i32 || g.in_dtype == DType::u32;
+  const char* acc_t = integer ? "unsigned int" : "float";
+  o << "  " << acc_t << " acc = 0;\n";
   o << "  for (long long k = 0; k < " << g.k << "ll; ++k) {\n";
-  o << "    const float av = " << loadConv(g.in_dtype, "a[k * " + std::to_string(g.a_stride_k) + "ll]") << ";\n";
-  o << "    const float bv = " <<  loadConv(g.b_dtype, "b[k * " + std::to_string(g.b_stride_k) + "ll]") << ";\n";
-  o << "    const float prod = av * bv;\n    acc = acc + prod;\n  }\n";
+  o << "    const " << acc_t << " av = " << (integer ? "(unsigned int)" : "") << loadConv(g.in_dtype, "a[k * " + std::to_string(g.a_stride_k) + "ll]") << ";\n";
+  o << "    const " << acc_t << " bv = " << (integer ? "(unsigned int)" : "") << loadConv(g.b_dtype, "b[k * " + std::to_string(g.b_stride_k) + "ll]") << ";\n";
+  o << "    const " << acc_t << " prod = av * bv;\n    acc = acc + prod;\n  }\n";
   std::string result = emitEpilogueBody(g.epilogue, o, "  ", "acc", "bi", "mi", "ni", "");
   o << "  C[idx] = " << storeConv(g.out_dtype, result) << ";\n}\n";
   KernelSource ks;
@@ -250,7 +254,7 @@ static void emitGemmSimtTiled(const GemmOp& g, const std::string& name, Plan& pl
 void emitGemm(const GemmOp& g, const std::string& name, Plan& plan, const ScheduleOverrides& o) {
   if (g.in_dtype == DType::f64) throw PlanError("f64 dot_general is not supported");
   if (g.tensor_core) emitGemmTcgen05(g, name, plan, o);
-  else if (g.batch * g.m * g.n >= 4096 && g.k >= 8) emitGemmSimtTiled(g, name, plan);   // tiny ones: one thread per output
+  else if (g.batch * g.m * g.n >= 4096 && g.k >= 8 && g.in_dtype != DType::i32 && g.in_dtype != DType::u32) emitGemmSimtTiled(g, name, plan);   // tiny ones: one thread per output
   else emitGemmSimt(g, name, plan);
 }
 

@@ -787,7 +787,8 @@ class Planner {
     GemmOp g;
     fillGemmOperands(op, g);
     g.out_dtype = P.typeOf(root).dtype;
-    if (g.in_dtype != DType::f32 && g.in_dtype != DType::bf16 && g.in_dtype != DType::f16)
+    const bool integer = (g.in_dtype == DType::i32 || g.in_dtype == DType::u32) && g.b_dtype == g.in_dtype && g.out_dtype == g.in_dtype;
+    if (g.in_dtype != DType::f32 && g.in_dtype != DType::bf16 && g.in_dtype != DType::f16 && !integer)
       throw PlanError(std::string("dot_general element type not supported: ") + dtypeName(g.in_dtype));
     DotShape s = canonicalDot(op);
     if (epilogue) {
@@ -865,6 +866,9 @@ class Planner {
     }
     if (dots.size() != 1) return false;
     uint32_t dot = *dots.begin();
+    // integer contractions run alone (exact wrap-around arithmetic in the SIMT kernel); what
+    // follows them is an ordinary elementwise kernel
+    if (P.ops[dot].result.dtype == DType::i32 || P.ops[dot].result.dtype == DType::u32) return false;
     Build b;
     b.root = v;
     b.trial = true;

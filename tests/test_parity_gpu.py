@@ -141,6 +141,24 @@ def test_f32_matmul_is_bit_exact(gpu_session, name):
     assert np.array_equal(out[:size].view(np.float32).view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("dtype", ["i32", "u32"])
+def test_integer_contraction_wraps_like_the_oracle(gpu_session, dtype):
+    """i32 / u32 contractions (the reference's dot lowering takes them) with values large enough
+    to overflow: exact wrap-around arithmetic, followed by an elementwise op in its own kernel."""
+    np_t = np.int32 if dtype == "i32" else np.uint32
+    program = tensor.define("int_dot_" + dtype, [tensor.spec(dtype, g=2, m=40, k=33), tensor.spec(dtype, g=2, k=33, n=50),
+                                                  tensor.spec(dtype, n=50)],
+                            lambda b, a: a[0].contract(a[1], "k").add(a[2]))
+    rng = np.random.default_rng(23)
+    inputs = [rng.integers(0, 2 ** 31 - 1, shape, dtype=np.int64).astype(np_t) for shape in ((2, 40, 33), (2, 33, 50), (50,))]
+    compiled = gpu_session.compile(program)
+    out = np.empty(compiled.output_descriptors()[0].byte_size, np.uint8)
+    gpu_session.invoke(compiled, inputs, [out])
+    gpu_session.release(compiled)
+    want = oracle.run(program.wire, inputs, mode="ref")[0]
+    assert np.array_equal(out.view(np_t), np.asarray(want).astype(np_t).reshape(-1))
+
+
 RAGGED_GEMMS = {
     "ragged_all": ([tensor.spec("bf16", m=300, k=200), tensor.spec("bf16", k=200, n=392)], lambda b, a: a[0].contract(a[1], "k")),
     "ragged_bias_tanh": ([tensor.spec("bf16", m=1000, k=72), tensor.spec("bf16", k=72, n=1032), tensor.spec("bf16", n=1032)],

@@ -111,7 +111,9 @@ uint32_t accy_b200_session_invoke(accy_b200_session* session, uint64_t handle,
                                   const size_t* output_sizes, uint32_t output_count);
 /* The same launch on buffers already in device memory (the vtable's launch on caller-allocated
  * buffers, contract.zig:2048-2085): no copies, asynchronous on `stream` (a CUstream, or NULL for
- * the session's own stream).  Pointers must be 256-byte aligned. */
+ * the session's own stream).  Pointers must be 256-byte aligned.  Launches of one handle must not
+ * overlap on the device (put them on one stream or order them with events): they share the
+ * program's temporaries, scratch and work counters. */
 uint32_t accy_b200_session_invoke_device(accy_b200_session* session, uint64_t handle,
                                          const uint64_t* input_ptrs, uint32_t input_count,
                                          const uint64_t* output_ptrs, uint32_t output_count,

@@ -76,6 +76,9 @@ PROTOTYPES = {
     "accy_b200_builder_finish": (c_u32, [c_p, P(c_u32), c_u32, P(P(ctypes.c_uint8)), P(c_size)]),
     "accy_b200_wire_reencode": (c_u32, [c_p, c_size, c_p, c_size, P(c_size), c_p, c_size]),
     "accy_b200_wire_shard": (c_u32, [c_p, c_size, c_str, ctypes.c_int64, c_p, c_size, P(c_size), P(c_u32), c_p, c_size]),
+    "accy_b200_wire_grad": (c_u32, [c_p, c_size, P(c_u64), c_u32, c_u32, c_p, c_size, P(c_size), c_p, c_size]),
+    "accy_b200_wire_vmap": (c_u32, [c_p, c_size, ctypes.c_int64, P(ctypes.c_int64), c_u32, c_u32, c_str, c_p, c_size,
+                            P(c_size), c_p, c_size]),
     "accy_b200_wire_describe": (c_u32, [c_p, c_size, c_p, c_size, P(c_size)]),
     "accy_b200_mismatch_noalloc": (c_u32, [c_p, c_p, c_p, c_p, c_u64, c_u64, c_u32, c_p, c_p, c_size]),
     "accy_b200_test_use_fake_driver": (None, [ctypes.c_int32]),

@@ -470,6 +470,8 @@ class Planner {
   // ---------------------------------------------------------------------------------------
   // row kernels
   // ---------------------------------------------------------------------------------------
+  int cluster_depth = 0;  // nesting of planCluster calls (a region materialising what it reads)
+
   void planCluster(uint32_t v) {
     Build b;
     b.root = v;
@@ -481,11 +483,19 @@ class Planner {
       b.is_col.push_back(false);
       map[i] = static_cast<int>(i);
     }
+    struct Depth {
+      int& d;
+      explicit Depth(int& v) : d(v) { ++d; }
+      ~Depth() { --d; }
+    } depth(cluster_depth);
     int root_node = buildNode(b, v, map);
     // Sibling outputs with the root's own dims (e.g. a value and its slope, both sums over the
     // same axis) join this region, so inputs they share are read once (the reference's concat
-    // reduction, reduction.zig:346-420, serves the same purpose).
+    // reduction, reduction.zig:346-420, serves the same purpose).  Only a region planned for an
+    // output itself takes siblings: one planned while another region is being built (a value
+    // that region reads) could otherwise pull in the output that asked for it, without end.
     for (auto it = out_slot_of.rbegin(); it != out_slot_of.rend(); ++it) {
+      if (cluster_depth != 1) break;
       const uint32_t u = it->first;
       if (u == v || produced.count(u) || slot_of[u] >= 0 || b.closure.count(u)) continue;
       const Operation& uop = P.ops[u];
@@ -1096,6 +1106,10 @@ class Planner {
 // value over nothing: the init value itself, reduction.zig:839-863) or a contraction over an empty
 // axis (zeros).  Those two are re-recorded as broadcasts of a scalar; everything else is replayed
 // unchanged, after which no kernel ever reads an empty value.
+//
+// The same pass brings every contraction to the operand order the kernels take (the reference's
+// dot lowering accepts only that order, dot.zig:2117-2161; gradients of contractions produce the
+// others): the operands are transposed, which costs nothing when the strides still describe them.
 static Program withoutEmptyFolds(const Program& p) {
   Builder b(p.name);
   std::vector<uint32_t> now(p.ops.size(), 0);
@@ -1123,7 +1137,36 @@ static Program withoutEmptyFolds(const Program& p) {
           std::vector<uint8_t> zero(dtypeSize(op.result.dtype), 0);
           made = b.broadcastTo(b.constantBytes(Type{op.result.dtype, {}}, zero.data(), zero.size()), op.result.dims, {});
         } else {
-          made = b.dotGeneralOp(arg(0), arg(1), op.ints, op.rhs_contract, op.lhs_batch, op.rhs_batch);
+          // operands brought to [batch, free, contract] x [batch, contract, free] by transposes
+          // (views: the contraction reads them through strides); the result dims do not change
+          auto ordered = [&](uint32_t x, const std::vector<int64_t>& batch, const std::vector<int64_t>& contract,
+                             bool contract_last) {
+            const size_t rank = b.typeOf(x).rank();
+            std::vector<int64_t> perm = batch, free_axes;
+            for (size_t a = 0; a < rank; ++a) {
+              const int64_t axis = static_cast<int64_t>(a);
+              if (std::find(batch.begin(), batch.end(), axis) == batch.end() &&
+                  std::find(contract.begin(), contract.end(), axis) == contract.end())
+                free_axes.push_back(axis);
+            }
+            if (contract_last) perm.insert(perm.end(), free_axes.begin(), free_axes.end());
+            perm.insert(perm.end(), contract.begin(), contract.end());
+            if (!contract_last) perm.insert(perm.end(), free_axes.begin(), free_axes.end());
+            bool identity = true;
+            for (size_t a = 0; a < rank; ++a) identity = identity && perm[a] == static_cast<int64_t>(a);
+            return identity ? x : b.transposeBy(x, perm);
+          };
+          const uint32_t lhs = ordered(arg(0), op.lhs_batch, op.ints, true);
+          const uint32_t rhs = ordered(arg(1), op.rhs_batch, op.rhs_contract, false);
+          const size_t nb = op.lhs_batch.size(), nk = op.ints.size();
+          const size_t nm = b.typeOf(lhs).rank() - nb - nk;
+          std::vector<int64_t> batch_axes, lhs_contract, rhs_contract;
+          for (size_t i = 0; i < nb; ++i) batch_axes.push_back(static_cast<int64_t>(i));
+          for (size_t i = 0; i < nk; ++i) {
+            lhs_contract.push_back(static_cast<int64_t>(nb + nm + i));
+            rhs_contract.push_back(static_cast<int64_t>(nb + i));
+          }
+          made = b.dotGeneralOp(lhs, rhs, lhs_contract, rhs_contract, batch_axes, batch_axes);
         }
         break;
       default:
@@ -1143,7 +1186,17 @@ Plan planProgram(const Program& program, const ScheduleOverrides& overrides) {
     if (op.result.dtype == DType::key) throw PlanError("key-typed values are not supported by the B200 target");
     for (const Dim& d : op.result.dims) has_empty |= d.extent == 0;
   }
-  if (has_empty) {
+  bool reorder = false;
+  for (const Operation& op : program.ops) {
+    if (op.kind != Kind::dot_general) continue;
+    const size_t nb = op.lhs_batch.size(), nk = op.ints.size();
+    const size_t nm = program.typeOf(op.operands[0]).rank() - nb - nk;
+    for (size_t i = 0; i < nb; ++i)
+      reorder |= op.lhs_batch[i] != static_cast<int64_t>(i) || op.rhs_batch[i] != static_cast<int64_t>(i);
+    for (size_t i = 0; i < nk; ++i)
+      reorder |= op.ints[i] != static_cast<int64_t>(nb + nm + i) || op.rhs_contract[i] != static_cast<int64_t>(nb + i);
+  }
+  if (has_empty || reorder) {
     const Program rewritten = withoutEmptyFolds(program);
     Planner planner(rewritten, overrides);
     return planner.run();

@@ -155,6 +155,18 @@ class Builder {
   bool finished_ = false;
 };
 
+// ---- program transformations (src/tensor/grad.zig:19-49, src/tensor/batch.zig:14-47) ----
+// Gradient of the single scalar output with respect to the parameters `wrt` (parameter indices);
+// outputs = [value if keep_value,] one gradient per wrt entry.  Errors: GradientRequiresScalarOutput,
+// ParameterOutOfRange, DuplicateParameter, NonDifferentiableParameter, UnsupportedDerivative.
+Program gradProgram(const Program& src, const std::vector<size_t>& wrt, bool keep_value);
+// Runs the program over a new named axis of extent axis_size.  in_axes[i] = position of the new
+// axis in parameter i, or -1 for a parameter shared by all instances; every output gets the axis
+// at out_axis.  An empty axis_name picks "#batch" (with a number appended while that name is
+// taken).  Errors: InvalidDimension, InAxisCountMismatch, AxisOutOfRange.
+Program vmapProgram(const Program& src, int64_t axis_size, const std::vector<int64_t>& in_axes, size_t out_axis,
+                    const std::string& axis_name);
+
 // ---- "ACTP" v1 wire bytes (src/tensor/wire/format.zig, encode.zig, decode.zig) ----
 struct WireError : std::runtime_error {
   // name is one of BadMagic, UnsupportedVersion, UnknownTag, InvalidReference, TooManyOperands,

@@ -9,6 +9,7 @@
 #include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
 #include <memory>
 #include <mutex>
 #include <sstream>
@@ -955,6 +956,53 @@ uint32_t accy_b200_wire_shard(const uint8_t* actp, size_t length, const char* ax
   } catch (const std::exception& e) {
     return fail(ACCY_B200_INVALID_PROGRAM, e.what());
   }
+}
+
+namespace {
+uint32_t transformedBytes(const std::function<Program()>& make, uint8_t* out, size_t capacity, size_t* out_length, char* error,
+                          size_t error_capacity) {
+  auto fail = [&](uint32_t status, const char* what) {
+    if (error && error_capacity) {
+      std::strncpy(error, what, error_capacity - 1);
+      error[error_capacity - 1] = '\0';
+    }
+    return status;
+  };
+  try {
+    std::vector<uint8_t> bytes = encodeProgram(make());
+    if (out_length) *out_length = bytes.size();
+    if (bytes.size() > capacity) return fail(ACCY_B200_INVALID_BUFFER, "output buffer too small");
+    std::memcpy(out, bytes.data(), bytes.size());
+    return ACCY_B200_OK;
+  } catch (const std::exception& e) {
+    return fail(ACCY_B200_INVALID_PROGRAM, e.what());
+  }
+}
+}  // namespace
+
+uint32_t accy_b200_wire_grad(const uint8_t* actp, size_t length, const uint64_t* wrt, uint32_t wrt_count,
+                             uint32_t keep_value, uint8_t* out, size_t capacity, size_t* out_length, char* error,
+                             size_t error_capacity) {
+  return transformedBytes(
+      [&] {
+        Program p = decodeProgram(actp, length);
+        std::vector<size_t> indices;
+        for (uint32_t i = 0; i < wrt_count; ++i) indices.push_back(static_cast<size_t>(wrt[i]));
+        return gradProgram(p, indices, keep_value != 0);
+      },
+      out, capacity, out_length, error, error_capacity);
+}
+
+uint32_t accy_b200_wire_vmap(const uint8_t* actp, size_t length, int64_t axis_size, const int64_t* in_axes,
+                             uint32_t in_axis_count, uint32_t out_axis, const char* axis_name, uint8_t* out,
+                             size_t capacity, size_t* out_length, char* error, size_t error_capacity) {
+  return transformedBytes(
+      [&] {
+        Program p = decodeProgram(actp, length);
+        std::vector<int64_t> axes(in_axes, in_axes + in_axis_count);
+        return vmapProgram(p, axis_size, axes, out_axis, axis_name ? axis_name : "");
+      },
+      out, capacity, out_length, error, error_capacity);
 }
 
 uint32_t accy_b200_wire_describe(const uint8_t* actp, size_t length, char* out, size_t capacity, size_t* out_length) {

@@ -275,6 +275,85 @@ class Program:
     def deinit(self):
         pass
 
+    # -- derived programs (src/tensor/function.zig: grad / valueAndGrad / vmap return programs) --
+    def grad(self, wrt):
+        """tensor.grad (src/tensor/grad.zig:19-33): gradients of the one scalar output with respect
+        to the parameter indices `wrt`, in that order."""
+        return _derive_grad(self, wrt, keep_value=False)
+
+    def value_and_grad(self, wrt):
+        """tensor.valueAndGrad (src/tensor/grad.zig:35-49): outputs = value, then the gradients."""
+        return _derive_grad(self, wrt, keep_value=True)
+
+    def vmap(self, axis_size, in_axes, out_axis=0, axis_name=""):
+        """tensor.vmap (src/tensor/batch.zig:14-47).  in_axes: per input the position of the new
+        axis (`mapped_axis(k)` or an int) or None for an input shared by every instance."""
+        return _derive_vmap(self, axis_size, in_axes, out_axis, axis_name)
+
+
+def mapped_axis(index):
+    """batch.zig:29 `mapped`: the new axis sits at position `index` of that input."""
+    return int(index)
+
+
+def _transformed(call, program):
+    wire = program.wire
+    src = ctypes.create_string_buffer(wire, len(wire))
+    capacity = 4 * len(wire) + 65536
+    err = ctypes.create_string_buffer(512)
+    for _ in range(2):
+        out = ctypes.create_string_buffer(capacity)
+        n = ctypes.c_size_t()
+        status = call(ctypes.cast(src, ctypes.c_void_p), len(wire), ctypes.cast(out, ctypes.c_void_p), capacity,
+                      ctypes.byref(n), ctypes.cast(err, ctypes.c_void_p), 512)
+        if status == 4 and n.value > capacity:  # invalid_buffer: the derived program is larger
+            capacity = n.value
+            continue
+        break
+    if status:
+        name = err.value.decode(errors="replace")
+        if status == 1:
+            raise TensorError(name)
+        raise SessionError(status, name)
+    return out.raw[:n.value]
+
+
+def _derive_grad(program, wrt, keep_value):
+    wrt = [int(i) for i in wrt]
+    indices = (ctypes.c_uint64 * max(1, len(wrt)))(*wrt)
+
+    def call(src, length, out, capacity, n, err, err_capacity):
+        return lib.accy_b200_wire_grad(src, length, indices, len(wrt), 1 if keep_value else 0, out, capacity, n,
+                                       err, err_capacity)
+    wire = _transformed(call, program)
+    outputs = ([program.output_types[0]] if keep_value else []) + [program.input_types[i] for i in wrt]
+    return Program(program.name, wire, list(program.input_types), outputs)
+
+
+def _derive_vmap(program, axis_size, in_axes, out_axis, axis_name):
+    axes = [-1 if a is None else int(a) for a in in_axes]
+    c_axes = (ctypes.c_int64 * max(1, len(axes)))(*axes)
+
+    def call(src, length, out, capacity, n, err, err_capacity):
+        return lib.accy_b200_wire_vmap(src, length, int(axis_size), c_axes, len(axes), int(out_axis),
+                                       axis_name.encode(), out, capacity, n, err, err_capacity)
+    wire = _transformed(call, program)
+    name = axis_name
+    if not name:
+        taken = {d for t in program.input_types + program.output_types for d, _ in t.dims}
+        name, attempt = "#batch", 0
+        while name in taken:
+            attempt += 1
+            name = "#batch%d" % attempt
+
+    def widened(ty, at):
+        dims = list(ty.dims)
+        dims.insert(at, (name, int(axis_size)))
+        return Type(ty.dtype, dims)
+    inputs = [t if a < 0 else widened(t, a) for t, a in zip(program.input_types, axes)]
+    outputs = [widened(t, int(out_axis)) for t in program.output_types]
+    return Program(program.name, wire, inputs, outputs)
+
 
 def define(name, specs, body):
     """tensor.define (src/tensor/trace/define.zig:8-19): records `body` on placeholders."""

@@ -194,6 +194,27 @@ uint32_t accy_b200_wire_reencode(const uint8_t* actp, size_t length, uint8_t* ou
 uint32_t accy_b200_wire_shard(const uint8_t* actp, size_t length, const char* axis, int64_t extent, uint8_t* out,
                               size_t capacity, size_t* out_length, uint32_t* partial_sum, char* error,
                               size_t error_capacity);
+/* ---- program transformations (src/tensor/grad.zig:19-49 `grad` / `valueAndGrad`,
+ * src/tensor/batch.zig:14-47 `vmap`; src/tensor/function.zig chains them) ----
+ * Both take ACTP bytes and write the derived program's ACTP bytes to `out` (*out_length is set even
+ * when `capacity` is too small: INVALID_BUFFER, call again with a larger buffer).  A refusal
+ * returns INVALID_PROGRAM with the reference's error name in `error`: GradientRequiresScalarOutput,
+ * ParameterOutOfRange, DuplicateParameter, NonDifferentiableParameter, UnsupportedDerivative;
+ * InvalidDimension, InAxisCountMismatch, AxisOutOfRange.
+ *
+ * grad: the program must have one rank-0 floating-point output.  The derived program takes the
+ * same inputs and returns [the value, when keep_value != 0,] then the gradient with respect to
+ * each parameter index in `wrt`, in that order, each typed like its parameter. */
+uint32_t accy_b200_wire_grad(const uint8_t* actp, size_t length, const uint64_t* wrt, uint32_t wrt_count,
+                             uint32_t keep_value, uint8_t* out, size_t capacity, size_t* out_length, char* error,
+                             size_t error_capacity);
+/* vmap: runs the program once per index of a new axis of extent axis_size.  in_axes[i] is the
+ * position of the new axis in input i (batch.zig `mapped(axis)`), or -1 for an input shared by
+ * every instance (`.none`); every output carries the new axis at out_axis (outputs that do not
+ * depend on a mapped input are repeated along it).  axis_name NULL or "" selects "#batch". */
+uint32_t accy_b200_wire_vmap(const uint8_t* actp, size_t length, int64_t axis_size, const int64_t* in_axes,
+                             uint32_t in_axis_count, uint32_t out_axis, const char* axis_name, uint8_t* out,
+                             size_t capacity, size_t* out_length, char* error, size_t error_capacity);
 /* Operation list of decoded bytes as text, one op per line: "id kind dtype[name=extent,...] ...". */
 uint32_t accy_b200_wire_describe(const uint8_t* actp, size_t length, char* out, size_t capacity,
                                  size_t* out_length);

@@ -137,6 +137,7 @@ const char* kGemmTemplate = R"CUDA(
 #define K_TOTAL @K@ll
 #define BATCH @BATCH@ll
 #define B_N_MAJOR @B_N_MAJOR@
+#define A_M_MAJOR @A_M_MAJOR@
 #define GROUP_M @GROUP_M@
 #define A_STAGE_BYTES (BLOCK_M * BLOCK_K * 2)
 #define B_STAGE_BYTES (BLOCK_N * BLOCK_K * 2)
@@ -206,7 +207,14 @@ extern "C" __global__ void __launch_bounds__(192, 1)
           mbar_expect_tx(full, STAGE_BYTES);
           const unsigned int sa = smem_u32(smem + stage * STAGE_BYTES);
           const unsigned int sb = sa + A_STAGE_BYTES;
+#if A_M_MAJOR
+          // A is [k, m] with m contiguous (a transposed operand): one 64(m) x 64(k) box per 64 rows of the tile
+#pragma unroll
+          for (int j = 0; j < BLOCK_M / 64; ++j)
+            tma_load_3d(sa + j * (64 * BLOCK_K * 2), &map_a, full, (int)(mb * BLOCK_M + j * 64), (int)(kb * BLOCK_K), (int)b);
+#else
           tma_load_3d(sa, &map_a, full, (int)(kb * BLOCK_K), (int)(mb * BLOCK_M), (int)b);
+#endif
 #if B_N_MAJOR
           // B is [k, n] with n contiguous: one 64(n) x 64(k) box per 64 columns of the tile
 #pragma unroll
@@ -223,9 +231,10 @@ extern "C" __global__ void __launch_bounds__(192, 1)
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      // instruction descriptor: f32 accumulate, A and B format (0 = f16, 1 = bf16), A K-major, B major
+      // instruction descriptor: f32 accumulate, A and B format (0 = f16, 1 = bf16), A and B major
       // as given, N, M=128
-      const unsigned int idesc = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | ((unsigned int)B_N_MAJOR << 16) |
+      const unsigned int idesc = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | ((unsigned int)A_M_MAJOR << 15) |
+                                 ((unsigned int)B_N_MAJOR << 16) |
                                  ((unsigned int)(BLOCK_N >> 3) << 17) | ((unsigned int)(BLOCK_M >> 4) << 24);
       int stage = 0; unsigned int phase = 0;
       unsigned int it = 0;
@@ -241,7 +250,12 @@ extern "C" __global__ void __launch_bounds__(192, 1)
           const unsigned int sa = smem_u32(smem + stage * STAGE_BYTES);
           const unsigned int sb = sa + A_STAGE_BYTES;
           // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart
+#if A_M_MAJOR
+          // A: M-major, 64-row chunks 64*128 bytes apart (leading), 8-k-row groups 1024 bytes apart (stride)
+          const unsigned long long a_desc = smem_desc(sa, 64 * BLOCK_K * 2, 1024);
+#else
           const unsigned long long a_desc = smem_desc(sa, 16, 1024);
+#endif
 #if B_N_MAJOR
           // B: N-major, 64-column chunks 64*128 bytes apart (leading), 8-k-row groups 1024 bytes apart (stride)
           const unsigned long long b_desc = smem_desc(sb, 64 * BLOCK_K * 2, 1024);
@@ -251,7 +265,11 @@ extern "C" __global__ void __launch_bounds__(192, 1)
 #pragma unroll
           for (int k = 0; k < BLOCK_K / 16; ++k) {
             // advance 16 k-elements: 32 bytes inside a K-major row, 16 rows of 128 bytes when N-major
+#if A_M_MAJOR
+            const unsigned long long a_k = a_desc + (unsigned long long)((k * 16 * 128) >> 4);
+#else
             const unsigned long long a_k = a_desc + (unsigned long long)((k * 32) >> 4);
+#endif
 #if B_N_MAJOR
             const unsigned long long b_k = b_desc + (unsigned long long)((k * 16 * 128) >> 4);
 #else
@@ -333,6 +351,7 @@ void emitGemmTcgen05(const GemmOp& g, const std::string& name, Plan& plan, const
   const int block_n = (g.n % 256 == 0) ? 256 : 128;
   const int stages = block_n == 256 ? 4 : 6;
   const bool n_major = g.b_stride_n == 1 && g.n > 1;
+  const bool m_major = g.a_stride_k != 1 && g.a_stride_m == 1;
   if (g.out_dtype != DType::bf16 && g.out_dtype != DType::f16 && g.out_dtype != DType::f32)
     throw PlanError("tcgen05 GEMM output must be bf16, f16 or f32");
 
@@ -375,6 +394,7 @@ void emitGemmTcgen05(const GemmOp& g, const std::string& name, Plan& plan, const
   replaceAll(src, "@K@", std::to_string(g.k));
   replaceAll(src, "@BATCH@", std::to_string(g.batch));
   replaceAll(src, "@B_N_MAJOR@", n_major ? "1" : "0");
+  replaceAll(src, "@A_M_MAJOR@", m_major ? "1" : "0");
   replaceAll(src, "@GROUP_M@", "16");
   replaceAll(src, "@OUT_T@", storageTypeOf(g.out_dtype));
   replaceAll(src, "@EPI_PARAMS@", epilogueParams(g.epilogue));
@@ -412,9 +432,18 @@ void emitGemmTcgen05(const GemmOp& g, const std::string& name, Plan& plan, const
   a.tma.box[0] = 64;
   a.tma.box[1] = 128;
   a.tma.box[2] = 1;
+  if (m_major) {
+    a.tma.dims[0] = g.m;
+    a.tma.dims[1] = g.k;
+    a.tma.strides[0] = static_cast<uint64_t>(g.a_stride_k) * 2;
+    a.tma.strides[1] = static_cast<uint64_t>(g.batch > 1 ? g.a_stride_b : g.k * g.a_stride_k) * 2;
+    a.tma.box[0] = 64;
+    a.tma.box[1] = 64;
+  }
   l.args.push_back(a);
 
   KernelArg b = a;
+  b.tma.box[2] = 1;
   b.tma.slot = g.b_slot;
   if (n_major) {
     b.tma.dims[0] = g.n;

@@ -840,7 +840,8 @@ class Planner {
     g.out_dtype = plan.slots[g.c_slot].storage;
     // the tensor-core kernel takes ragged extents (TMA zero fill, guarded stores); what it needs
     // is at least one full tile per dimension and 16-byte row strides for the TMA descriptors
-    const bool aligned = g.m >= 128 && g.n >= 128 && g.k >= 64 && g.k % 8 == 0 && g.a_stride_k == 1 &&
+    const bool a_ok = g.a_stride_k == 1 || (g.a_stride_m == 1 && g.a_stride_k % 8 == 0 && g.a_stride_b % 8 == 0);
+    const bool aligned = g.m >= 128 && g.n >= 128 && g.k >= 64 && g.k % 8 == 0 && a_ok &&
                          ((g.b_stride_n == 1 && g.n % 8 == 0) || g.b_stride_k == 1);
     const bool half_inputs = (g.in_dtype == DType::bf16 && g.b_dtype == DType::bf16) || (g.in_dtype == DType::f16 && g.b_dtype == DType::f16);
     g.tensor_core = half_inputs && aligned && !ov.force_simt_gemm && tcgen05Ready();

@@ -167,6 +167,12 @@ RAGGED_GEMMS = {
     "batched_k_major_b": ([tensor.spec("bf16", g=3, m=200, k=136), tensor.spec("bf16", g=3, n=150, k=136)],
                           lambda b, a: a[0].contract(a[1], "k")),
     "f32_output_odd_n": ([tensor.spec("bf16", m=130, k=128), tensor.spec("bf16", n=131, k=128)], lambda b, a: a[0].contract(a[1], "k")),
+    # lhs stored [k, m] (what the gradient of a contraction with respect to its rhs reads): M-major A tiles
+    "transposed_a": ([tensor.spec("bf16", k=200, m=304), tensor.spec("bf16", k=200, n=392)], lambda b, a: a[0].contract(a[1], "k")),
+    "transposed_a_k_major_b": ([tensor.spec("bf16", k=136, m=264), tensor.spec("bf16", n=150, k=136)],
+                               lambda b, a: a[0].contract(a[1], "k")),
+    "batched_transposed_a": ([tensor.spec("bf16", g=2, k=128, m=200), tensor.spec("bf16", g=2, k=128, n=256)],
+                             lambda b, a: a[0].contract(a[1], "k")),
 }
 
 

@@ -420,3 +420,26 @@ def test_large_refine_program_on_the_device(gpu_session):
     # the slope is a cancelling sum of terms of size |time| * |gap|: compare on that scale
     scale = (2.0 * np.abs(gap * np.cos(phase)) * time.astype(np.float64)).sum(axis=1)
     assert np.max(np.abs(slope - want_slope) / scale) < 1e-5
+
+
+@pytest.mark.gpu
+def test_bf16_mlp_gradient_runs_on_tensor_cores(gpu_session):
+    """Every contraction of the gradient program (x^T g, g W^T, ...) stays on tcgen05: transposed
+    operands are read through strides (K-major or MN-major tiles), not copied."""
+    from accy_b200 import configs
+    specs = [T.spec("bf16", token=384, d=128), T.spec("bf16", d=128, h=256), T.spec("bf16", h=256, d=128)]
+    program = tensor.define("mlp_loss", specs, mlp_loss).grad([0, 1, 2])
+    rng = np.random.default_rng(21)
+    inputs = [configs.f32_to_bf16_bits((rng.standard_normal([e for _, e in sp.dims]) * scale).astype(np.float32))
+              for sp, scale in zip(specs, (1.0, 0.1, 0.1))]
+    compiled = gpu_session.compile(program)
+    summary = compiled.plan_summary()
+    assert summary.count("tcgen05") >= 5 and " simt" not in summary, summary
+    outs = [np.empty(d.byte_size, np.uint8) for d in compiled.output_descriptors()]
+    gpu_session.invoke(compiled, inputs, outs)
+    gpu_session.release(compiled)
+    for got_raw, want in zip(outs, oracle.run(program.wire, inputs, mode="wide")):
+        got = configs.bf16_bits_to_f32(got_raw.view(np.uint16)).astype(np.float64)
+        want64 = configs.bf16_bits_to_f32(want).reshape(-1).astype(np.float64)
+        rms = np.sqrt(np.mean(want64 ** 2))
+        assert np.max(np.abs(got - want64) / (np.abs(want64) + rms)) < 2e-2

@@ -351,7 +351,19 @@ class Planner {
           n.level = std::max(n.level, b.nodes[n.args[i]].level);
         }
         b.closure.insert(v);
-        int id = addNode(b, n);
+        int id = -1;
+        if (op.kind == Kind::binary && static_cast<Binary>(op.sub) == Binary::mul &&
+            (n.dtype == DType::f32 || n.dtype == DType::f64)) {
+          // x * 1 is x, bit for bit (signed zeros, infinities and NaNs included): the gradient
+          // transformation multiplies by its seed of ones
+          const uint64_t one = n.dtype == DType::f32 ? 0x3f800000ull : 0x3ff0000000000000ull;
+          for (int side = 0; side < 2 && id < 0; ++side) {
+            const ENode& k = b.nodes[n.args[side]];
+            if (k.op == ENode::Const && k.dtype == n.dtype && k.bits == one && b.nodes[n.args[1 - side]].dtype == n.dtype)
+              id = n.args[1 - side];
+          }
+        }
+        if (id < 0) id = addNode(b, n);
         if (is_output[v] && v != b.root && !produced.count(v)) b.coproduce.push_back({v, id});
         return id;
       }

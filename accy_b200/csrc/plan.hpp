@@ -176,7 +176,8 @@ struct ShardInfo {
   std::string axis;
   int64_t extent = -1;          // the axis' extent in the program
   bool shardable = false;
-  bool partial_sum = false;     // pieces produce partial sums of every output (add them up)
+  bool partial_sum = false;     // pieces produce partial folds of every output (combine them)
+  uint32_t partial_fold = 0;    // how: 1 = add, 2 = maximum, 3 = minimum (the outputs' own reducer)
   std::vector<uint32_t> partial_outputs;
   std::string reason;           // why not, when !shardable
 };

@@ -947,7 +947,7 @@ uint32_t accy_b200_wire_shard(const uint8_t* actp, size_t length, const char* ax
     Program piece = shardProgram(p, axis ? axis : "", extent);
     std::vector<uint8_t> bytes = encodeProgram(piece);
     if (out_length) *out_length = bytes.size();
-    if (partial_sum) *partial_sum = info.partial_sum ? 1u : 0u;
+    if (partial_sum) *partial_sum = info.partial_sum ? info.partial_fold : 0u;
     if (bytes.size() > capacity) return fail(ACCY_B200_INVALID_BUFFER, "output buffer too small");
     std::memcpy(out, bytes.data(), bytes.size());
     return ACCY_B200_OK;

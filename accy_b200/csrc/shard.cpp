@@ -70,9 +70,15 @@ ShardInfo analyseShardAxis(const Program& p, const std::string& axis) {
         const Type& in = p.typeOf(op.operands[0]);
         for (int64_t d : op.ints)
           if (in.dims[d].name == axis) {
-            // allowed only as the program's final sum
-            if (is_output[op.id] && static_cast<Reducer>(op.sub) == Reducer::sum) {
+            // allowed only as the program's final fold: the pieces' results combine with the
+            // same reducer (sum: one all-reduce that adds; max / min: one that takes the extreme)
+            const uint32_t fold = 1u + static_cast<uint32_t>(op.sub);
+            if (is_output[op.id] && (info.partial_fold == 0 || info.partial_fold == fold)) {
+              info.partial_fold = fold;
               info.partial_outputs.push_back(op.id);
+            } else if (is_output[op.id]) {
+              info.reason = "outputs fold the axis with different reducers";
+              return info;
             } else {
               info.reason = "the axis is reduced inside the program";
               return info;
@@ -107,7 +113,7 @@ ShardInfo analyseShardAxis(const Program& p, const std::string& axis) {
   for (uint32_t part : info.partial_outputs)
     for (const Operation& op : p.ops)
       for (uint32_t a : op.operands)
-        if (a == part) { info.reason = "a partial sum over the axis is used inside the program"; return info; }
+        if (a == part) { info.reason = "a partial fold over the axis is used inside the program"; return info; }
   for (uint32_t id : p.outputs) {
     const Type& t = p.typeOf(id);
     long at = findDim(t.dims, axis);
@@ -122,7 +128,7 @@ ShardInfo analyseShardAxis(const Program& p, const std::string& axis) {
   info.partial_sum = !info.partial_outputs.empty();
   if (info.partial_sum && info.partial_outputs.size() != p.outputs.size()) {
     info.shardable = false;
-    info.reason = "only some outputs are sums over the axis";
+    info.reason = "only some outputs are folds over the axis";
   }
   return info;
 }

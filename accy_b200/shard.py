@@ -4,8 +4,8 @@ The reference executes on a single device and has no collective of any kind, so 
 no counterpart there.  A program is cut along a named batch-like axis with
 `tensor.shard_program`; each rank compiles the piece for its own block of the axis and runs it on
 its own rows, with no exchange between ranks.  Only when the chosen axis is the one the program
-sums over do the ranks hold partial sums, which one all-reduce adds up (NCCL on GPUs, gloo in the
-CPU tests of the host logic).
+folds over (sum, max or min as its last step) do the ranks hold partial results, which one
+all-reduce with the same operation combines (NCCL on GPUs, gloo in the CPU tests of the host logic).
 """
 import numpy as np
 
@@ -73,7 +73,7 @@ class ShardedCuda:
     def launch(self, local_inputs, local_outputs):
         self.executor.launch(local_inputs, local_outputs)
         if self.plan.partial_sum and self.plan.world > 1:
-            all_reduce_partials(local_outputs, self.plan.piece.output_types, self.group)
+            all_reduce_partials(local_outputs, self.plan.piece.output_types, self.group, fold=self.plan.partial_sum.name)
 
     def deinit(self):
         self.executor.deinit()
@@ -82,8 +82,9 @@ class ShardedCuda:
 _TORCH_DTYPES = {"f32": "float32", "f64": "float64", "i32": "int32", "i64": "int64"}
 
 
-def all_reduce_partials(outputs, types, group=None):
-    """Adds the per-rank partial sums in place: one all-reduce per output buffer."""
+def all_reduce_partials(outputs, types, group=None, fold="sum"):
+    """Combines the per-rank partial results in place: one all-reduce per output buffer, adding
+    them or taking their maximum / minimum (`fold`, ShardPlan.partial_sum.name)."""
     import torch
     import torch.distributed as dist
     for buf, ty in zip(outputs, types):
@@ -93,4 +94,5 @@ def all_reduce_partials(outputs, types, group=None):
             t = buf.view(getattr(torch, _TORCH_DTYPES[ty.dtype]))
         else:
             t = torch.from_numpy(np.asarray(buf).reshape(-1).view(getattr(np, _TORCH_DTYPES[ty.dtype])))
-        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+        op = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[fold]
+        dist.all_reduce(t, op=op, group=group)

@@ -367,12 +367,20 @@ def define(name, specs, body):
     return Program(name, wire, input_types, output_types)
 
 
+class PartialFold(int):
+    """How the pieces' outputs combine: 0 (falsy) = independent blocks, 1 = add, 2 = maximum, 3 = minimum."""
+
+    @property
+    def name(self):
+        return (None, "sum", "max", "min")[int(self)]
+
+
 def shard_program(program, axis, extent):
     """Re-records `program` with `extent` for the named axis so it can run as independent pieces
     (one rank per GPU, or one chunk at a time).  Returns (piece, partial_sum): when partial_sum
     is True every output of a piece is a partial sum over the axis and the pieces must be added
     (one all-reduce); otherwise piece i's outputs are rows [i*extent, (i+1)*extent) of the full
-    outputs.  Raises SessionError("compile_failed") when an operation mixes values across the axis."""
+    outputs (partial_sum.name says how the pieces combine: "sum", "max" or "min").  Raises SessionError("compile_failed") when an operation mixes values across the axis."""
     wire = program.wire if isinstance(program, Program) else bytes(program)
     src = ctypes.create_string_buffer(wire, len(wire))
     out = ctypes.create_string_buffer(len(wire) + 65536)
@@ -391,7 +399,7 @@ def shard_program(program, axis, extent):
     name = program.name if isinstance(program, Program) else "shard"
     inputs = resize(program.input_types) if isinstance(program, Program) else []
     outputs = resize(program.output_types) if isinstance(program, Program) else []
-    return Program(name, piece_wire, inputs, outputs), bool(partial.value)
+    return Program(name, piece_wire, inputs, outputs), PartialFold(partial.value)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -189,8 +189,9 @@ uint32_t accy_b200_wire_reencode(const uint8_t* actp, size_t length, uint8_t* ou
 /* Re-records a program with extent `extent` for the named axis, for running it as independent
  * pieces (one per GPU, or one per chunk).  No counterpart in the reference, which runs on one
  * device.  Refused (COMPILE_FAILED, reason in `error`) when an operation mixes values across the
- * axis.  *partial_sum = 1 when the program's outputs are sums over the axis: the pieces' outputs
- * must then be added (one all-reduce). */
+ * axis.  *partial_sum is 0 when piece i's outputs are block i of the full outputs; 1, 2 or 3 when
+ * every output is a sum, maximum or minimum over the axis: the pieces' outputs must then be
+ * combined with that operation (one all-reduce). */
 uint32_t accy_b200_wire_shard(const uint8_t* actp, size_t length, const char* axis, int64_t extent, uint8_t* out,
                               size_t capacity, size_t* out_length, uint32_t* partial_sum, char* error,
                               size_t error_capacity);

@@ -31,7 +31,7 @@ def _rank_main(rank, world, port, case, result_dir):
         local = plan.local_inputs(rank, inputs)
         outs = oracle.run(plan.piece.wire, [bytes(b) for b in local])
         if plan.partial_sum:
-            shard.all_reduce_partials(outs, plan.piece.output_types)
+            shard.all_reduce_partials(outs, plan.piece.output_types, fold=plan.partial_sum.name)
         np.save(os.path.join(result_dir, "rank%d.npy" % rank), outs[0])
         with open(os.path.join(result_dir, "rank%d.txt" % rank), "w") as f:
             f.write("%d %s %s" % (int(plan.partial_sum), plan.output_slices(rank), plan.input_slices(rank)))
@@ -44,10 +44,29 @@ def _case(name):
         return configs.softmax_layernorm(8, 64), "row"
     if name == "guesses":
         return configs.mismatch(6, 128), "guess"
+    if name == "column_maxima":
+        return _ColumnExtreme("max"), "row"
+    if name == "column_minima":
+        return _ColumnExtreme("min"), "row"
     return configs.mismatch(6, 128), "point"
 
 
-@pytest.mark.parametrize("case", ["rows", "guesses", "points"])
+class _ColumnExtreme:
+    """max / min over the sharded axis: the ranks' partial extremes combine with the same operation"""
+
+    def __init__(self, which):
+        self.which = which
+
+    def program(self):
+        from accy_b200 import tensor
+        return tensor.define("column_" + self.which, [tensor.spec("f32", row=8, col=16)],
+                             lambda b, a: getattr(a[0], self.which)("row"))
+
+    def make_inputs(self):
+        return [np.random.default_rng(3).standard_normal((8, 16)).astype(np.float32)]
+
+
+@pytest.mark.parametrize("case", ["rows", "guesses", "points", "column_maxima", "column_minima"])
 def test_two_ranks_reproduce_the_single_device_result(case, tmp_path):
     import torch.multiprocessing as mp
     world = 2
@@ -55,7 +74,10 @@ def test_two_ranks_reproduce_the_single_device_result(case, tmp_path):
     cfg, axis = _case(case)
     full = oracle.run(cfg.program().wire, cfg.make_inputs())[0]
     parts = [np.load(os.path.join(str(tmp_path), "rank%d.npy" % r)) for r in range(world)]
-    if case == "points":
+    if case.startswith("column_"):
+        # extremes are exact whatever the split
+        assert np.array_equal(parts[0], full) and np.array_equal(parts[1], full)
+    elif case == "points":
         # the summed axis was split: every rank holds the all-reduced total
         for p in parts:
             assert np.allclose(p, full, rtol=1e-5)

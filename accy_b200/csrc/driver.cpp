@@ -58,6 +58,12 @@ void loadReal() {
   bind(lib, g_real.cuEventElapsedTime, "cuEventElapsedTime");
   bind(lib, g_real.cuGetErrorName, "cuGetErrorName");
   bind(lib, g_real.cuTensorMapEncodeTiled, "cuTensorMapEncodeTiled");
+  bind(lib, g_real.cuStreamBeginCapture, "cuStreamBeginCapture_v2");
+  bind(lib, g_real.cuStreamEndCapture, "cuStreamEndCapture");
+  bind(lib, g_real.cuGraphInstantiateWithFlags, "cuGraphInstantiateWithFlags");
+  bind(lib, g_real.cuGraphLaunch, "cuGraphLaunch");
+  bind(lib, g_real.cuGraphExecDestroy, "cuGraphExecDestroy");
+  bind(lib, g_real.cuGraphDestroy, "cuGraphDestroy");
   CUresult_t r = g_real.cuInit(0);
   if (r != 0) throw std::runtime_error("cuInit failed: " + std::to_string(r));
   g_real_loaded = true;
@@ -132,13 +138,28 @@ CUresult_t f_cuTensorMapEncodeTiled(TensorMap* m, int, unsigned, void*, const ui
   return fakeResult("cuTensorMapEncodeTiled");
 }
 
+CUresult_t f_cuStreamBeginCapture(CUstream_t, int) { return fakeResult("cuStreamBeginCapture"); }
+CUresult_t f_cuStreamEndCapture(CUstream_t, CUgraph_t* g) {
+  *g = reinterpret_cast<CUgraph_t>(0x6000);
+  return fakeResult("cuStreamEndCapture");
+}
+CUresult_t f_cuGraphInstantiateWithFlags(CUgraphExec_t* e, CUgraph_t, unsigned long long) {
+  *e = reinterpret_cast<CUgraphExec_t>(0x7000);
+  return fakeResult("cuGraphInstantiateWithFlags");
+}
+CUresult_t f_cuGraphLaunch(CUgraphExec_t, CUstream_t) { return fakeResult("cuGraphLaunch"); }
+CUresult_t f_cuGraphExecDestroy(CUgraphExec_t) { return fakeResult("cuGraphExecDestroy"); }
+CUresult_t f_cuGraphDestroy(CUgraph_t) { return fakeResult("cuGraphDestroy"); }
+
 const DriverTable g_fake = {
     f_cuInit, f_cuDeviceGet, f_cuDeviceGetCount, f_cuDeviceGetAttribute, f_cuDevicePrimaryCtxRetain,
     f_cuDevicePrimaryCtxRelease, f_cuCtxSetCurrent, f_cuModuleLoadData, f_cuModuleUnload,
     f_cuModuleGetFunction, f_cuFuncSetAttribute, f_cuLaunchKernel, f_cuMemAlloc, f_cuMemFree,
     f_cuMemcpyHtoDAsync, f_cuMemcpyDtoHAsync, f_cuMemsetD8Async, f_cuStreamCreate, f_cuStreamDestroy,
     f_cuStreamSynchronize, f_cuStreamWaitEvent, f_cuEventCreate, f_cuEventDestroy, f_cuEventRecord,
-    f_cuEventSynchronize, f_cuEventElapsedTime, f_cuGetErrorName, f_cuTensorMapEncodeTiled};
+    f_cuEventSynchronize, f_cuEventElapsedTime, f_cuGetErrorName, f_cuTensorMapEncodeTiled,
+    f_cuStreamBeginCapture, f_cuStreamEndCapture, f_cuGraphInstantiateWithFlags, f_cuGraphLaunch,
+    f_cuGraphExecDestroy, f_cuGraphDestroy};
 
 // ---- NVRTC ----
 struct Nvrtc {

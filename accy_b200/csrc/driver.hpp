@@ -21,6 +21,8 @@ typedef struct CUmod_st* CUmodule_t;
 typedef struct CUfunc_st* CUfunction_t;
 typedef struct CUstream_st* CUstream_t;
 typedef struct CUevent_st* CUevent_t;
+typedef struct CUgraph_st* CUgraph_t;
+typedef struct CUgraphExec_st* CUgraphExec_t;
 
 struct alignas(64) TensorMap {
   uint64_t opaque[16];
@@ -59,6 +61,14 @@ struct DriverTable {
                                        const uint64_t* dims, const uint64_t* strides,
                                        const uint32_t* box, const uint32_t* elem_strides,
                                        int interleave, int swizzle, int l2, int oob);
+  // launch sequences recorded once and replayed (the reference's record_sequence / submit_sequence,
+  // deps/lib/compiler/gpu/src/contract.zig:1929-1966)
+  CUresult_t (*cuStreamBeginCapture)(CUstream_t, int mode);
+  CUresult_t (*cuStreamEndCapture)(CUstream_t, CUgraph_t*);
+  CUresult_t (*cuGraphInstantiateWithFlags)(CUgraphExec_t*, CUgraph_t, unsigned long long flags);
+  CUresult_t (*cuGraphLaunch)(CUgraphExec_t, CUstream_t);
+  CUresult_t (*cuGraphExecDestroy)(CUgraphExec_t);
+  CUresult_t (*cuGraphDestroy)(CUgraph_t);
 };
 
 // Returns the active table: the real driver (loaded on first call) or the fake.  Throws

@@ -48,6 +48,11 @@ struct Entry {
   std::vector<std::vector<std::string>> names;  // descriptor name storage
   CUevent_t ev_begin = nullptr, ev_end = nullptr;
   bool timed = false;
+  // The launch list recorded once as a CUDA graph and replayed while the bound pointers stay the
+  // same (a host invoke always binds the program's own buffers).
+  CUgraphExec_t graph = nullptr;
+  std::vector<CUdeviceptr_t> graph_bound;
+  int graph_recordings = 0;              // re-recordings so far; callers that change pointers every time stop being recorded
   // Chunked host invoke: the program re-recorded for a slice of its outermost batch-like axis,
   // loaded three times (three lanes = three streams with their own buffers) so that the copy in
   // of chunk i+1, the kernels of chunk i and the copy out of chunk i-1 overlap.
@@ -364,17 +369,59 @@ struct accy_b200_session {
         if (k.module) d.cuModuleUnload(k.module);
       if (e.ev_begin) d.cuEventDestroy(e.ev_begin);
       if (e.ev_end) d.cuEventDestroy(e.ev_end);
+      if (e.graph) d.cuGraphExecDestroy(e.graph);
     }
     uint32_t generation = e.generation + 1;
     e = Entry{};
     e.generation = generation;
   }
 
-  // Launches the plan with e.bound holding a device pointer for every slot.
+  // Launches the plan with e.bound holding a device pointer for every slot.  A plan of several
+  // kernels is recorded as a CUDA graph on its first single-shot launch and replayed afterwards
+  // (one submission instead of one per kernel; the reference's record_sequence / submit_sequence,
+  // deps/lib/compiler/gpu/src/contract.zig:1929-1966).  ACCY_B200_NO_GRAPHS=1 turns this off.
   void launchAll(Entry& e, CUstream_t on, bool time_it) {
     if (poisoned) throw StatusError{ACCY_B200_LAUNCH_FAILED, "session is poisoned by an earlier failed launch"};
     const DriverTable& d = driver();
     if (time_it) check(d.cuEventRecord(e.ev_begin, on), "cuEventRecord");
+    static const bool graphs_off = std::getenv("ACCY_B200_NO_GRAPHS") != nullptr;
+    const bool replayable = time_it && !graphs_off && e.plan.launches.size() >= 2 && e.graph_recordings < 4;
+    bool submitted = false;
+    if (replayable && e.graph && e.graph_bound == e.bound) {
+      submitted = d.cuGraphLaunch(e.graph, on) == 0;
+      if (!submitted) e.graph_recordings = 4;  // give up on graphs for this program, launch directly below
+    } else if (replayable && d.cuStreamBeginCapture(on, 2 /* relaxed: other threads' calls do not matter */) == 0) {
+      if (e.graph) d.cuGraphExecDestroy(e.graph);
+      e.graph = nullptr;
+      e.graph_recordings += 1;
+      CUgraph_t recorded = nullptr;
+      try {
+        issueLaunches(e, on);
+      } catch (...) {
+        d.cuStreamEndCapture(on, &recorded);
+        if (recorded) d.cuGraphDestroy(recorded);
+        throw;
+      }
+      if (d.cuStreamEndCapture(on, &recorded) == 0 && recorded &&
+          d.cuGraphInstantiateWithFlags(&e.graph, recorded, 0) == 0 && d.cuGraphLaunch(e.graph, on) == 0) {
+        e.graph_bound = e.bound;
+        submitted = true;
+      } else {
+        if (e.graph) d.cuGraphExecDestroy(e.graph);
+        e.graph = nullptr;
+        e.graph_recordings = 4;
+      }
+      if (recorded) d.cuGraphDestroy(recorded);
+    }
+    if (!submitted) issueLaunches(e, on);
+    if (time_it) {
+      check(d.cuEventRecord(e.ev_end, on), "cuEventRecord");
+      e.timed = true;
+    }
+  }
+
+  void issueLaunches(Entry& e, CUstream_t on) {
+    const DriverTable& d = driver();
     for (const Launch& l : e.plan.launches) {
       std::vector<uint64_t> values(l.args.size());
       std::vector<std::unique_ptr<TensorMap>> maps;
@@ -406,10 +453,6 @@ struct accy_b200_session {
         poisoned = true;
         throw StatusError{ACCY_B200_LAUNCH_FAILED, "cuLaunchKernel(" + l.label + ") failed: " + driverErrorName(r)};
       }
-    }
-    if (time_it) {
-      check(d.cuEventRecord(e.ev_end, on), "cuEventRecord");
-      e.timed = true;
     }
   }
 };

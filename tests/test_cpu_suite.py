@@ -340,6 +340,35 @@ def test_invoke_flow_on_the_fake_driver(fake_driver):
     session.deinit()
 
 
+def test_multi_kernel_programs_replay_a_recorded_launch_sequence(fake_driver):
+    """A plan of several kernels is captured as a CUDA graph by its first host invoke and replayed
+    by the following ones: the kernels are enqueued once, later invokes submit the graph only."""
+    session = tensor.Session(device=0)
+    program = tensor.define("two_stage", [tensor.spec("f32", a=50, b=70)], lambda b, a: a[0].sum("b").max("a"))
+    compiled = session.compile(program)
+    launches = compiled.work()["launches"]
+    assert launches >= 2
+    count = lambda name: lib.accy_b200_test_fake_call_count(name)
+    before = {n: count(n) for n in (b"cuLaunchKernel", b"cuGraphLaunch", b"cuStreamBeginCapture", b"cuGraphInstantiateWithFlags")}
+    x = np.ones((50, 70), np.float32)
+    out = np.zeros(1, np.float32)
+    for _ in range(3):
+        session.invoke(compiled, [x], [out])
+    assert count(b"cuLaunchKernel") - before[b"cuLaunchKernel"] == launches
+    assert count(b"cuStreamBeginCapture") - before[b"cuStreamBeginCapture"] == 1
+    assert count(b"cuGraphInstantiateWithFlags") - before[b"cuGraphInstantiateWithFlags"] == 1
+    assert count(b"cuGraphLaunch") - before[b"cuGraphLaunch"] == 3
+    # a failed replay falls back to plain launches and stops using the graph
+    lib.accy_b200_test_fake_fail(b"cuGraphLaunch", 0)
+    session.invoke(compiled, [x], [out])
+    lib.accy_b200_test_fake_fail(b"cuGraphLaunch", -1)
+    assert count(b"cuLaunchKernel") - before[b"cuLaunchKernel"] == 2 * launches
+    session.invoke(compiled, [x], [out])
+    assert count(b"cuLaunchKernel") - before[b"cuLaunchKernel"] == 3 * launches
+    session.release(compiled)
+    session.deinit()
+
+
 def test_resident_inputs_are_copied_once(fake_driver):
     """set_resident uploads an input once; invokes that pass None for it copy only the others,
     a wrong size is refused, and dropping the copy makes None invalid again."""

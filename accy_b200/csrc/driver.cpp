@@ -2,6 +2,9 @@
 #include "driver.hpp"
 
 #include <dlfcn.h>
+#include <unistd.h>
+
+#include <cstdio>
 
 #include <cstdlib>
 #include <cstring>
@@ -171,6 +174,7 @@ struct Nvrtc {
   int (*getProgramLog)(void*, char*);
   int (*destroyProgram)(void**);
   const char* (*getErrorString)(int);
+  int (*version)(int*, int*);
   bool loaded = false;
 } g_nvrtc;
 
@@ -197,6 +201,7 @@ void loadNvrtc() {
   bind(lib, g_nvrtc.getProgramLog, "nvrtcGetProgramLog");
   bind(lib, g_nvrtc.destroyProgram, "nvrtcDestroyProgram");
   bind(lib, g_nvrtc.getErrorString, "nvrtcGetErrorString");
+  bind(lib, g_nvrtc.version, "nvrtcVersion");
   g_nvrtc.loaded = true;
 }
 
@@ -247,7 +252,66 @@ std::mutex g_cubin_mutex;
 std::map<std::string, std::vector<char>> g_cubins;
 size_t g_cubin_bytes = 0;
 constexpr size_t kCubinCacheLimit = 256u << 20;
+
+// The same cache on disk, for the next process: ACCY_B200_KERNEL_CACHE_DIR names a directory
+// (nothing is written anywhere unless it is set).  One file per kernel, named by a hash of the
+// compiler version, options and source; the file repeats that text in full and is used only if
+// it matches, so a hash collision or a truncated file costs a recompilation, never a wrong kernel.
+const char kDiskMagic[8] = {'A', 'C', 'C', 'Y', 'C', 'U', 'B', '1'};
+
+std::string diskPath(const std::string& key) {
+  const char* dir = getenv("ACCY_B200_KERNEL_CACHE_DIR");
+  if (!dir || !*dir) return "";
+  uint64_t h1 = 1469598103934665603ull, h2 = 0x9e3779b97f4a7c15ull;
+  for (unsigned char ch : key) {
+    h1 = (h1 ^ ch) * 1099511628211ull;
+    h2 = (h2 + ch) * 0xff51afd7ed558ccdull;
+    h2 ^= h2 >> 29;
+  }
+  char name[64];
+  std::snprintf(name, sizeof name, "/accy_%016llx%016llx.cubin", static_cast<unsigned long long>(h1),
+                static_cast<unsigned long long>(h2));
+  return std::string(dir) + name;
+}
+
+bool readDisk(const std::string& path, const std::string& key, std::vector<char>* cubin) {
+  FILE* f = std::fopen(path.c_str(), "rb");
+  if (!f) return false;
+  bool ok = false;
+  char magic[8];
+  uint64_t key_size = 0, cubin_size = 0;
+  if (std::fread(magic, 1, 8, f) == 8 && std::memcmp(magic, kDiskMagic, 8) == 0 &&
+      std::fread(&key_size, 8, 1, f) == 1 && std::fread(&cubin_size, 8, 1, f) == 1 && key_size == key.size() &&
+      cubin_size > 0 && cubin_size <= kCubinCacheLimit) {
+    std::string stored(key_size, '\0');
+    cubin->resize(cubin_size);
+    ok = std::fread(&stored[0], 1, key_size, f) == key_size && stored == key &&
+         std::fread(cubin->data(), 1, cubin_size, f) == cubin_size && std::fgetc(f) == EOF;
+  }
+  std::fclose(f);
+  return ok;
+}
+
+void writeDisk(const std::string& path, const std::string& key, const std::vector<char>& cubin) {
+  // written under a private name and renamed into place, so a reader never sees half a file
+  const std::string tmp = path + ".tmp" + std::to_string(static_cast<long long>(getpid()));
+  FILE* f = std::fopen(tmp.c_str(), "wb");
+  if (!f) return;
+  const uint64_t key_size = key.size(), cubin_size = cubin.size();
+  bool ok = std::fwrite(kDiskMagic, 1, 8, f) == 8 && std::fwrite(&key_size, 8, 1, f) == 1 &&
+            std::fwrite(&cubin_size, 8, 1, f) == 1 && std::fwrite(key.data(), 1, key.size(), f) == key.size() &&
+            std::fwrite(cubin.data(), 1, cubin.size(), f) == cubin.size();
+  ok = std::fclose(f) == 0 && ok;
+  if (!ok || std::rename(tmp.c_str(), path.c_str()) != 0) std::remove(tmp.c_str());
+}
+
+unsigned g_nvrtc_runs = 0;
 }  // namespace
+
+unsigned nvrtcCompileCount() {
+  std::lock_guard<std::mutex> lock(g_cubin_mutex);
+  return g_nvrtc_runs;
+}
 
 std::vector<char> compileToCubin(const std::string& source, const std::string& name,
                                  const std::vector<std::string>& extra_options, std::string* log) {
@@ -257,8 +321,11 @@ std::vector<char> compileToCubin(const std::string& source, const std::string& n
   }
   const char* no_cache = getenv("ACCY_B200_NO_KERNEL_CACHE");
   const bool cached = !(no_cache && *no_cache == '1');
-  std::string key;
+  std::string key, disk;
   if (cached) {
+    int major = 0, minor = 0;
+    g_nvrtc.version(&major, &minor);
+    key = "nvrtc " + std::to_string(major) + "." + std::to_string(minor) + '\n';
     for (const std::string& o : extra_options) key += o + '\n';
     key += '\0';
     key += source;
@@ -268,6 +335,18 @@ std::vector<char> compileToCubin(const std::string& source, const std::string& n
       if (log) log->clear();
       return hit->second;
     }
+    disk = diskPath(key);
+    std::vector<char> stored;
+    if (!disk.empty() && readDisk(disk, key, &stored)) {
+      if (log) log->clear();
+      if (g_cubin_bytes + stored.size() + key.size() <= kCubinCacheLimit && g_cubins.emplace(key, stored).second)
+        g_cubin_bytes += stored.size() + key.size();
+      return stored;
+    }
+  }
+  {
+    std::lock_guard<std::mutex> lock(g_cubin_mutex);
+    g_nvrtc_runs += 1;
   }
   void* prog = nullptr;
   int rc = g_nvrtc.createProgram(&prog, source.c_str(), (name + ".cu").c_str(), 0, nullptr, nullptr);
@@ -295,6 +374,7 @@ std::vector<char> compileToCubin(const std::string& source, const std::string& n
     std::lock_guard<std::mutex> lock(g_cubin_mutex);
     if (g_cubin_bytes + cubin.size() + key.size() <= kCubinCacheLimit && g_cubins.emplace(key, cubin).second)
       g_cubin_bytes += cubin.size() + key.size();
+    if (!disk.empty()) writeDisk(disk, key, cubin);
   }
   return cubin;
 }

@@ -80,6 +80,7 @@ unsigned fakeCallCount(const std::string& function);
 std::string driverErrorName(CUresult_t r);
 
 // NVRTC: CUDA source -> sm_100a cubin.  Throws std::runtime_error carrying the compiler log.
+unsigned nvrtcCompileCount();  // NVRTC runs so far in this process (cache hits do not count)
 std::vector<char> compileToCubin(const std::string& source, const std::string& name,
                                  const std::vector<std::string>& extra_options, std::string* log);
 

@@ -1078,6 +1078,8 @@ void accy_b200_test_fake_fail(const char* driver_function, int32_t after_calls) 
   fakeFailAfter(driver_function ? driver_function : "", after_calls);
 }
 uint32_t accy_b200_test_fake_call_count(const char* driver_function) {
+  // "nvrtcCompileProgram" counts real NVRTC runs of this process (cache hits, in memory or on disk, do not)
+  if (driver_function && std::strcmp(driver_function, "nvrtcCompileProgram") == 0) return nvrtcCompileCount();
   return fakeCallCount(driver_function ? driver_function : "");
 }
 

@@ -413,6 +413,33 @@ def test_compiled_kernels_are_reused_across_sessions():
     assert spent[1] * 5 < spent[0]
 
 
+def test_compiled_kernels_are_reused_across_processes(tmp_path):
+    """ACCY_B200_KERNEL_CACHE_DIR keeps compiled kernels on disk: a second process compiles the same
+    program without running NVRTC; a damaged file is ignored and rewritten."""
+    import subprocess
+    import sys
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "from accy_b200 import tensor, configs\n"
+            "from accy_b200._native import lib\n"
+            "s = tensor.Session(device=-1)\n"
+            "c = s.compile(configs.mismatch(5, 4111).program())\n"
+            "print('nvrtc_runs', lib.accy_b200_test_fake_call_count(b'nvrtcCompileProgram'))\n") % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, ACCY_B200_KERNEL_CACHE_DIR=str(tmp_path))
+
+    def runs():
+        out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0, out.stderr
+        return int(out.stdout.split("nvrtc_runs")[1])
+    assert runs() >= 1
+    files = sorted(tmp_path.glob("accy_*.cubin"))
+    assert files and not list(tmp_path.glob("*.tmp*"))
+    assert runs() == 0
+    files[0].write_bytes(files[0].read_bytes()[:100])
+    assert runs() >= 1
+    assert files[0].stat().st_size > 100
+    assert runs() == 0
+
+
 def test_failed_launch_poisons_the_session(fake_driver):
     session = tensor.Session(device=0)
     cfg = configs.mismatch(8, 16)

@@ -572,6 +572,46 @@ class Cuda:
         self.session.deinit()
 
 
+class Function:
+    """tensor.Function (src/tensor/function.zig:10-83): a recording together with the programs
+    derived from it.  `grad`, `value_and_grad` and `vmap` return Functions that the root keeps, so
+    one `deinit` on the root releases them all; `compile_cuda` stands where `compileCpu` does."""
+
+    def __init__(self, program, root=None):
+        self.graph = program
+        self.root = root
+        self.derived = []
+
+    @classmethod
+    def define(cls, name, specs, body):
+        return cls(define(name, specs, body))
+
+    def _adopt(self, program):
+        root = self.root or self
+        child = Function(program, root)
+        root.derived.append(child)
+        return child
+
+    def grad(self, wrt):
+        return self._adopt(self.graph.grad(wrt))
+
+    def value_and_grad(self, wrt):
+        return self._adopt(self.graph.value_and_grad(wrt))
+
+    def vmap(self, axis_size, in_axes, out_axis=0, axis_name=""):
+        return self._adopt(self.graph.vmap(axis_size, in_axes, out_axis, axis_name))
+
+    def compile_cuda(self, device=0, **overrides):
+        return Cuda(self.graph, device=device, **overrides)
+
+    def deinit(self):
+        assert self.root is None, "derived functions are released by their root"
+        for child in self.derived:
+            child.graph.deinit()
+        self.derived = []
+        self.graph.deinit()
+
+
 def run_cuda(program, inputs, outputs, device=0):
     """runCpu's contract (src/tensor/execute.zig:54-63) on a B200: compile, run, free."""
     executor = Cuda(program, device=device)

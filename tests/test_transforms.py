@@ -81,6 +81,35 @@ def test_refine_eight_frequency_guesses_with_the_oracle():
     check_descent(*descend(lambda f: oracle.run(each.wire, [f, time, sample])))
 
 
+def test_function_keeps_its_derived_programs():
+    """src/tensor/function.zig: derived functions hang off the root, whatever they were derived from."""
+    f = tensor.Function.define("mismatch", [T.spec("f32"), T.spec("f32", point=16), T.spec("f32", point=16)], mismatch)
+    both = f.value_and_grad([0])
+    each = both.vmap(8, [T.mapped_axis(0), None, None], axis_name="guess")
+    assert both.root is f and each.root is f and f.derived == [both, each]
+    assert each.graph.wire == refine_program().wire
+    with pytest.raises(AssertionError):
+        each.deinit()
+    f.deinit()
+    assert f.derived == []
+
+
+@pytest.mark.gpu
+def test_function_compile_cuda_runs_the_readme_example():
+    f = tensor.Function.define("mismatch", [T.spec("f32"), T.spec("f32", point=16), T.spec("f32", point=16)], mismatch)
+    each = f.value_and_grad([0]).vmap(8, [T.mapped_axis(0), None, None], axis_name="guess")
+    cuda = each.compile_cuda()
+    time, sample = tone_samples()
+    value, slope = np.empty(8, np.float32), np.empty(8, np.float32)
+
+    def run(frequency):
+        cuda.launch([frequency, time, sample], [value, slope])
+        return value.copy(), slope.copy()
+    check_descent(*descend(run))
+    cuda.deinit()
+    f.deinit()
+
+
 @pytest.mark.gpu
 def test_refine_eight_frequency_guesses_on_the_device(gpu_session):
     each = refine_program()

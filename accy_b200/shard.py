@@ -95,4 +95,10 @@ def all_reduce_partials(outputs, types, group=None, fold="sum"):
         else:
             t = torch.from_numpy(np.asarray(buf).reshape(-1).view(getattr(np, _TORCH_DTYPES[ty.dtype])))
         op = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[fold]
-        dist.all_reduce(t, op=op, group=group)
+        if not t.is_cuda and "nccl" in str(dist.get_backend(group)):
+            # host buffers (what `launch` fills) with an NCCL group: the collective runs on device memory
+            staged = t.cuda()
+            dist.all_reduce(staged, op=op, group=group)
+            t.copy_(staged)
+        else:
+            dist.all_reduce(t, op=op, group=group)

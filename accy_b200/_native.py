@@ -77,6 +77,7 @@ PROTOTYPES = {
     "accy_b200_wire_reencode": (c_u32, [c_p, c_size, c_p, c_size, P(c_size), c_p, c_size]),
     "accy_b200_wire_shard": (c_u32, [c_p, c_size, c_str, ctypes.c_int64, c_p, c_size, P(c_size), P(c_u32), c_p, c_size]),
     "accy_b200_wire_grad": (c_u32, [c_p, c_size, P(c_u64), c_u32, c_u32, c_p, c_size, P(c_size), c_p, c_size]),
+    "accy_b200_wire_jvp": (c_u32, [c_p, c_size, P(c_u64), c_u32, c_p, c_size, P(c_size), c_p, c_size]),
     "accy_b200_wire_vmap": (c_u32, [c_p, c_size, ctypes.c_int64, P(ctypes.c_int64), c_u32, c_u32, c_str, c_p, c_size,
                             P(c_size), c_p, c_size]),
     "accy_b200_wire_describe": (c_u32, [c_p, c_size, c_p, c_size, P(c_size)]),

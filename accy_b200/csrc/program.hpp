@@ -160,6 +160,9 @@ class Builder {
 // outputs = [value if keep_value,] one gradient per wrt entry.  Errors: GradientRequiresScalarOutput,
 // ParameterOutOfRange, DuplicateParameter, NonDifferentiableParameter, UnsupportedDerivative.
 Program gradProgram(const Program& src, const std::vector<size_t>& wrt, bool keep_value);
+// Forward mode (src/tensor/autodiff.zig:725-732 `jvp`): inputs = the source's, then one tangent per
+// differentiated parameter in parameter order; outputs = the source's, then their tangents.
+Program jvpProgram(const Program& src, const std::vector<size_t>& wrt);
 // Runs the program over a new named axis of extent axis_size.  in_axes[i] = position of the new
 // axis in parameter i, or -1 for a parameter shared by all instances; every output gets the axis
 // at out_axis.  An empty axis_name picks "#batch" (with a number appended while that name is

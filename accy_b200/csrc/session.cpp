@@ -1036,6 +1036,18 @@ uint32_t accy_b200_wire_grad(const uint8_t* actp, size_t length, const uint64_t*
       out, capacity, out_length, error, error_capacity);
 }
 
+uint32_t accy_b200_wire_jvp(const uint8_t* actp, size_t length, const uint64_t* wrt, uint32_t wrt_count, uint8_t* out,
+                            size_t capacity, size_t* out_length, char* error, size_t error_capacity) {
+  return transformedBytes(
+      [&] {
+        Program p = decodeProgram(actp, length);
+        std::vector<size_t> indices;
+        for (uint32_t i = 0; i < wrt_count; ++i) indices.push_back(static_cast<size_t>(wrt[i]));
+        return jvpProgram(p, indices);
+      },
+      out, capacity, out_length, error, error_capacity);
+}
+
 uint32_t accy_b200_wire_vmap(const uint8_t* actp, size_t length, int64_t axis_size, const int64_t* in_axes,
                              uint32_t in_axis_count, uint32_t out_axis, const char* axis_name, uint8_t* out,
                              size_t capacity, size_t* out_length, char* error, size_t error_capacity) {

@@ -364,6 +364,197 @@ Program gradProgram(const Program& src, const std::vector<size_t>& wrt, bool kee
 }
 
 // ---------------------------------------------------------------------------------------------
+// jvp: forward mode (src/tensor/autodiff.zig:86-742)
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// Tangents are carried beside the primal values; a value nothing differentiable reaches has none
+// (the reference records explicit zeros and prunes "structural zeros", autodiff.zig:346-352).
+class Forward {
+ public:
+  Forward(const Program& src, Builder& b, const std::vector<size_t>& wrt) : src_(src), b_(b) {
+    now_.assign(src.ops.size(), 0);
+    tan_.assign(src.ops.size(), std::nullopt);
+    // all primal parameters first, then one tangent parameter per differentiated parameter, in
+    // parameter order (autodiff.zig:178-203)
+    for (uint32_t id : src.parameters) now_[id] = replayUnchanged(b, src.ops[id], now_);
+    for (uint32_t id : src.parameters) {
+      const Operation& op = src.ops[id];
+      if (std::find(wrt.begin(), wrt.end(), op.index) == wrt.end()) continue;
+      tan_[id] = b.input(op.result.dtype, op.result.dims, /*authored=*/false);
+    }
+    for (const Operation& op : src.ops) {
+      if (op.kind == Kind::parameter) continue;
+      now_[op.id] = replayUnchanged(b, op, now_);
+      push(op);
+    }
+  }
+
+  uint32_t primal(uint32_t id) const { return now_[id]; }
+  uint32_t tangent(uint32_t id) { return tan_[id] ? *tan_[id] : filled(b_, src_.typeOf(id), 0.0); }
+
+ private:
+  using Opt = std::optional<uint32_t>;
+  uint32_t bin(Binary op, uint32_t l, uint32_t r) { return b_.binary(op, l, r); }
+  uint32_t neg(uint32_t x) { return b_.unary(Unary::neg, x); }
+  uint32_t zerosLike(uint32_t id) { return filled(b_, src_.typeOf(id), 0.0); }
+  static void needFloat(const Type& t) {
+    if (!dtypeIsFloat(t.dtype)) throw TensorError("UnsupportedDerivative");
+  }
+
+  void push(const Operation& op) {
+    auto t = [&](size_t i) -> Opt { return tan_[op.operands[i]]; };
+    auto x = [&](size_t i) { return now_[op.operands[i]]; };
+    const uint32_t y = now_[op.id];
+    switch (op.kind) {
+      case Kind::unary: {
+        if (!t(0)) return;
+        needFloat(src_.typeOf(op.operands[0]));
+        const Type& ty = src_.typeOf(op.operands[0]);
+        const uint32_t d = *t(0);
+        switch (static_cast<Unary>(op.sub)) {
+          case Unary::neg: tan_[op.id] = neg(d); return;
+          case Unary::exp: tan_[op.id] = bin(Binary::mul, y, d); return;
+          case Unary::log: tan_[op.id] = bin(Binary::div, d, x(0)); return;
+          case Unary::sqrt: tan_[op.id] = bin(Binary::div, d, bin(Binary::mul, filled(b_, ty, 2.0), y)); return;
+          case Unary::tanh:
+            tan_[op.id] = bin(Binary::mul, d, bin(Binary::sub, filled(b_, ty, 1.0), bin(Binary::mul, y, y)));
+            return;
+          case Unary::sin: tan_[op.id] = bin(Binary::mul, d, b_.unary(Unary::cos, x(0))); return;
+          case Unary::cos: tan_[op.id] = neg(bin(Binary::mul, d, b_.unary(Unary::sin, x(0)))); return;
+          case Unary::abs:
+            tan_[op.id] = b_.select(b_.compare(Compare::ge, x(0), filled(b_, ty, 0.0)), d, neg(d));
+            return;
+          case Unary::tan: {
+            uint32_t c = b_.unary(Unary::cos, x(0));
+            tan_[op.id] = bin(Binary::div, d, bin(Binary::mul, c, c));
+            return;
+          }
+        }
+        return;
+      }
+      case Kind::binary: {
+        const Opt tl = t(0), tr = t(1);
+        if (!tl && !tr) return;
+        needFloat(src_.typeOf(op.operands[0]));
+        const uint32_t l = x(0), r = x(1);
+        switch (static_cast<Binary>(op.sub)) {
+          case Binary::add: tan_[op.id] = tl && tr ? bin(Binary::add, *tl, *tr) : (tl ? *tl : tr.value()); return;
+          case Binary::sub: tan_[op.id] = tl && tr ? bin(Binary::sub, *tl, *tr) : (tl ? *tl : neg(tr.value())); return;
+          case Binary::mul: {
+            Opt a = tl ? Opt(bin(Binary::mul, *tl, r)) : std::nullopt;
+            Opt c = tr ? Opt(bin(Binary::mul, l, *tr)) : std::nullopt;
+            tan_[op.id] = a && c ? bin(Binary::add, *a, *c) : (a ? *a : c.value());
+            return;
+          }
+          case Binary::div: {
+            Opt a = tl ? Opt(bin(Binary::mul, *tl, r)) : std::nullopt;
+            Opt c = tr ? Opt(bin(Binary::mul, l, *tr)) : std::nullopt;
+            uint32_t numerator = a && c ? bin(Binary::sub, *a, *c) : (a ? *a : neg(c.value()));
+            tan_[op.id] = bin(Binary::div, numerator, bin(Binary::mul, r, r));
+            return;
+          }
+          case Binary::max:
+          case Binary::min: {
+            Compare dir = static_cast<Binary>(op.sub) == Binary::max ? Compare::ge : Compare::le;
+            uint32_t zeros = filled(b_, op.result, 0.0);
+            tan_[op.id] = b_.select(b_.compare(dir, l, r), tl ? *tl : zeros, tr ? *tr : zeros);
+            return;
+          }
+          case Binary::pow: {
+            Opt base, exponent;
+            if (tl) {
+              uint32_t step_down = bin(Binary::pow, l, bin(Binary::sub, r, filled(b_, op.result, 1.0)));
+              base = bin(Binary::mul, bin(Binary::mul, r, step_down), *tl);
+            }
+            if (tr) exponent = bin(Binary::mul, bin(Binary::mul, bin(Binary::pow, l, r), b_.unary(Unary::log, l)), *tr);
+            tan_[op.id] = base && exponent ? bin(Binary::add, *base, *exponent) : (base ? *base : exponent.value());
+            return;
+          }
+        }
+        return;
+      }
+      case Kind::select: {
+        const Opt tt = t(1), tf = t(2);
+        if (!tt && !tf) return;
+        uint32_t zeros = filled(b_, op.result, 0.0);
+        tan_[op.id] = b_.select(x(0), tt ? *tt : zeros, tf ? *tf : zeros);
+        return;
+      }
+      case Kind::broadcast_in_dim:
+        if (t(0)) tan_[op.id] = b_.broadcastTo(*t(0), op.result.dims, op.ints);
+        return;
+      case Kind::reshape:
+        if (t(0)) tan_[op.id] = b_.reshapeTo(*t(0), op.result.dims);
+        return;
+      case Kind::transpose:
+        if (t(0)) tan_[op.id] = b_.transposeBy(*t(0), op.ints);
+        return;
+      case Kind::reduce: {
+        const Opt tx = t(0), ti = t(1);
+        if (!tx && !ti) return;
+        const Type& in = src_.typeOf(op.operands[0]);
+        needFloat(in);
+        const Reducer red = static_cast<Reducer>(op.sub);
+        const uint32_t zero = b_.fullFloat(Type{in.dtype, {}}, 0.0);
+        if (red == Reducer::sum) {
+          tan_[op.id] = b_.reduce(tx ? *tx : zerosLike(op.operands[0]), ti ? *ti : zero, Reducer::sum, op.ints);
+          return;
+        }
+        const std::vector<int64_t> kept = keptAxes(in.rank(), op.ints);
+        Opt from_input, from_init;
+        if (tx) {
+          uint32_t mask = b_.compare(Compare::eq, x(0), b_.broadcastTo(y, in.dims, kept));
+          from_input = b_.reduce(b_.select(mask, *tx, zerosLike(op.operands[0])), zero, Reducer::sum, op.ints);
+        }
+        if (ti) {
+          auto everywhere = [&](uint32_t v) { return op.result.rank() == 0 ? v : b_.broadcastTo(v, op.result.dims, {}); };
+          uint32_t mask = b_.compare(Compare::eq, y, everywhere(x(1)));
+          from_init = b_.select(mask, everywhere(*ti), filled(b_, op.result, 0.0));
+        }
+        tan_[op.id] = from_input && from_init ? bin(Binary::add, *from_input, *from_init) : (from_input ? *from_input : from_init.value());
+        return;
+      }
+      case Kind::dot_general: {
+        const Opt tl = t(0), tr = t(1);
+        if (!tl && !tr) return;
+        needFloat(src_.typeOf(op.operands[0]));
+        Opt left = tl ? Opt(b_.dotGeneralOp(*tl, x(1), op.ints, op.rhs_contract, op.lhs_batch, op.rhs_batch)) : std::nullopt;
+        Opt right = tr ? Opt(b_.dotGeneralOp(x(0), *tr, op.ints, op.rhs_contract, op.lhs_batch, op.rhs_batch)) : std::nullopt;
+        tan_[op.id] = left && right ? bin(Binary::add, *left, *right) : (left ? *left : right.value());
+        return;
+      }
+      default: return;  // constant, iota, compare: no tangent
+    }
+  }
+
+  const Program& src_;
+  Builder& b_;
+  std::vector<uint32_t> now_;
+  std::vector<Opt> tan_;
+};
+
+}  // namespace
+
+Program jvpProgram(const Program& src, const std::vector<size_t>& wrt) {
+  for (size_t i = 0; i < wrt.size(); ++i) {
+    if (wrt[i] >= src.parameters.size()) throw TensorError("ParameterOutOfRange");
+    for (size_t j = 0; j < i; ++j)
+      if (wrt[j] == wrt[i]) throw TensorError("DuplicateParameter");
+    if (!dtypeIsFloat(src.typeOf(src.parameters[wrt[i]]).dtype)) throw TensorError("NonDifferentiableParameter");
+  }
+  Builder b(src.name);
+  Forward pass(src, b, wrt);
+  std::vector<uint32_t> outputs;
+  for (uint32_t id : src.outputs) outputs.push_back(pass.primal(id));
+  for (uint32_t id : src.outputs) {
+    if (!dtypeIsFloat(src.typeOf(id).dtype)) throw TensorError("UnsupportedDerivative");
+    outputs.push_back(pass.tangent(id));
+  }
+  return b.finish(outputs);
+}
+
+// ---------------------------------------------------------------------------------------------
 // vmap
 // ---------------------------------------------------------------------------------------------
 namespace {

@@ -285,6 +285,18 @@ class Program:
         """tensor.valueAndGrad (src/tensor/grad.zig:35-49): outputs = value, then the gradients."""
         return _derive_grad(self, wrt, keep_value=True)
 
+    def jvp(self, wrt):
+        """tensor.jvp (src/tensor/autodiff.zig:725-732): inputs + one tangent per parameter in `wrt`
+        (parameter order); outputs + their tangents."""
+        wrt = [int(i) for i in wrt]
+        indices = (ctypes.c_uint64 * max(1, len(wrt)))(*wrt)
+
+        def call(src, length, out, capacity, n, err, err_capacity):
+            return lib.accy_b200_wire_jvp(src, length, indices, len(wrt), out, capacity, n, err, err_capacity)
+        wire = _transformed(call, self)
+        inputs = list(self.input_types) + [self.input_types[i] for i in sorted(wrt)]
+        return Program(self.name, wire, inputs, list(self.output_types) * 2)
+
     def vmap(self, axis_size, in_axes, out_axis=0, axis_name=""):
         """tensor.vmap (src/tensor/batch.zig:14-47).  in_axes: per input the position of the new
         axis (`mapped_axis(k)` or an int) or None for an input shared by every instance."""
@@ -597,6 +609,9 @@ class Function:
 
     def value_and_grad(self, wrt):
         return self._adopt(self.graph.value_and_grad(wrt))
+
+    def jvp(self, wrt):
+        return self._adopt(self.graph.jvp(wrt))
 
     def vmap(self, axis_size, in_axes, out_axis=0, axis_name=""):
         return self._adopt(self.graph.vmap(axis_size, in_axes, out_axis, axis_name))

@@ -209,6 +209,12 @@ uint32_t accy_b200_wire_shard(const uint8_t* actp, size_t length, const char* ax
 uint32_t accy_b200_wire_grad(const uint8_t* actp, size_t length, const uint64_t* wrt, uint32_t wrt_count,
                              uint32_t keep_value, uint8_t* out, size_t capacity, size_t* out_length, char* error,
                              size_t error_capacity);
+/* jvp (src/tensor/autodiff.zig:725-732): forward mode, any number and rank of outputs.  The derived
+ * program takes the source's inputs followed by one tangent per parameter listed in `wrt` (in
+ * parameter order, typed like the parameter) and returns the source's outputs followed by their
+ * tangents (zeros for an output no listed parameter reaches). */
+uint32_t accy_b200_wire_jvp(const uint8_t* actp, size_t length, const uint64_t* wrt, uint32_t wrt_count, uint8_t* out,
+                            size_t capacity, size_t* out_length, char* error, size_t error_capacity);
 /* vmap: runs the program once per index of a new axis of extent axis_size.  in_axes[i] is the
  * position of the new axis in input i (batch.zig `mapped(axis)`), or -1 for an input shared by
  * every instance (`.none`); every output carries the new axis at out_axis (outputs that do not

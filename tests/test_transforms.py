@@ -296,6 +296,54 @@ def test_transform_error_names():
 
 
 # ---------------------------------------------------------------------------------------------
+# jvp (forward mode) against the gradient and against finite differences
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", sorted(GRAD_CASES))
+def test_jvp_agrees_with_the_gradient(name):
+    """For a scalar program the tangent along direction v is the sum over parameters of <grad, v>."""
+    program, shapes, wrt = define_case(name, "f64")
+    inputs = grad_inputs(name, shapes, np.float64)
+    forward = program.jvp(wrt)
+    ordered = sorted(wrt)                      # tangent inputs come in parameter order
+    assert [repr(t) for t in forward.input_types] == [repr(t) for t in program.input_types] + \
+        [repr(program.input_types[i]) for i in ordered]
+    assert len(forward.output_types) == 2
+    rng = np.random.default_rng(17)
+    directions = [rng.uniform(-1.0, 1.0, inputs[i].shape) for i in ordered]
+    value, tangent = oracle.run(forward.wire, inputs + directions)
+    assert scalar(value) == pytest.approx(scalar(oracle.run(program.wire, inputs)[0]), rel=1e-14)
+    gradients = oracle.run(program.grad(ordered).wire, inputs)
+    expected = sum(float(np.sum(g.reshape(-1) * d.reshape(-1))) for g, d in zip(gradients, directions))
+    scale = sum(float(np.sum(np.abs(g.reshape(-1) * d.reshape(-1)))) for g, d in zip(gradients, directions))
+    assert abs(scalar(tangent) - expected) < 1e-11 * max(scale, 1e-3)
+
+
+def test_jvp_of_a_program_with_several_array_outputs():
+    def body(b, a):
+        x, w = a
+        e = x.sub(x.max("c")).exp()
+        return [e.div(e.sum("c")), x.contract(w, "c").tanh(), w.mul(w)]
+    specs = [T.spec("f64", r=4, c=6), T.spec("f64", c=6, k=3)]
+    program = tensor.define("several", specs, body)
+    rng = np.random.default_rng(2)
+    x, w = rng.uniform(-1, 1, (4, 6)), rng.uniform(-1, 1, (6, 3))
+    dx = rng.uniform(-1, 1, (4, 6))
+    forward = program.jvp([0])
+    assert len(forward.input_types) == 3 and len(forward.output_types) == 6
+    outs = oracle.run(forward.wire, [x, w, dx])
+    h = 1e-6
+    up = oracle.run(program.wire, [x + h * dx, w])
+    down = oracle.run(program.wire, [x - h * dx, w])
+    for primal, tangent, u, d, plain in zip(outs[:3], outs[3:], up, down, oracle.run(program.wire, [x, w])):
+        np.testing.assert_allclose(primal, plain, rtol=1e-14)
+        np.testing.assert_allclose(tangent, (u - d) / (2 * h), rtol=1e-6, atol=1e-8)
+    assert not outs[5].any()                  # w*w does not depend on x: its tangent is zeros
+    with pytest.raises(tensor.TensorError) as info:
+        program.jvp([2])
+    assert info.value.name == "ParameterOutOfRange"
+
+
+# ---------------------------------------------------------------------------------------------
 # vmap against one run per index
 # ---------------------------------------------------------------------------------------------
 def row_softmax(b, a):
@@ -377,10 +425,17 @@ def test_vmap_default_axis_name():
 # ---------------------------------------------------------------------------------------------
 # the derived programs on the CUDA target
 # ---------------------------------------------------------------------------------------------
-DEVICE_CASES = sorted(GRAD_CASES) + sorted(VMAP_CASES)
+JVP_DEVICE_CASES = ["jvp_attention", "jvp_mlp", "jvp_binary_zoo", "jvp_extrema"]
+DEVICE_CASES = sorted(GRAD_CASES) + sorted(VMAP_CASES) + JVP_DEVICE_CASES
 
 
 def derived_case(name):
+    if name.startswith("jvp_"):
+        program, shapes, wrt = define_case(name[4:], "f32")
+        inputs = grad_inputs(name[4:], shapes, np.float32)
+        rng = np.random.default_rng(23)
+        directions = [rng.uniform(-1.0, 1.0, inputs[i].shape).astype(np.float32) for i in sorted(wrt)]
+        return program.jvp(wrt), inputs + directions
     if name in GRAD_CASES:
         program, shapes, wrt = define_case(name, "f32")
         return program.value_and_grad(wrt), grad_inputs(name, shapes, np.float32)

@@ -294,8 +294,7 @@ class Program:
         def call(src, length, out, capacity, n, err, err_capacity):
             return lib.accy_b200_wire_jvp(src, length, indices, len(wrt), out, capacity, n, err, err_capacity)
         wire = _transformed(call, self)
-        inputs = list(self.input_types) + [self.input_types[i] for i in sorted(wrt)]
-        return Program(self.name, wire, inputs, list(self.output_types) * 2)
+        return Program(self.name, wire, *_io_types(wire))
 
     def vmap(self, axis_size, in_axes, out_axis=0, axis_name=""):
         """tensor.vmap (src/tensor/batch.zig:14-47).  in_axes: per input the position of the new
@@ -330,6 +329,35 @@ def _transformed(call, program):
     return out.raw[:n.value]
 
 
+def _io_types(wire):
+    """(input types, output types) of ACTP bytes, read back from the library's own decoding
+    (accy_b200_wire_describe: one "id kind dtype[name=extent,...] operands" line per operation,
+    then "outputs %id ...")."""
+    src = ctypes.create_string_buffer(wire, len(wire))
+    capacity = 64 * len(wire) + 65536
+    out = ctypes.create_string_buffer(capacity)
+    n = ctypes.c_size_t()
+    status = lib.accy_b200_wire_describe(ctypes.cast(src, ctypes.c_void_p), len(wire), ctypes.cast(out, ctypes.c_void_p),
+                                         capacity, ctypes.byref(n))
+    if status:
+        raise SessionError(status, "cannot describe the derived program")
+    types, inputs, outputs = {}, [], []
+    for line in out.raw[:n.value].decode().splitlines():
+        fields = line.split(" ")
+        if fields[0] == "outputs":
+            outputs = [types[int(f[1:])] for f in fields[1:]]
+            continue
+        dtype, _, rest = fields[2].partition("[")
+        dims = []
+        for item in filter(None, rest.rstrip("]").split(",")):
+            name, _, extent = item.rpartition("=")
+            dims.append((name, int(extent)))
+        types[int(fields[0])] = Type(dtype, dims)
+        if fields[1] == "parameter":
+            inputs.append(types[int(fields[0])])
+    return inputs, outputs
+
+
 def _derive_grad(program, wrt, keep_value):
     wrt = [int(i) for i in wrt]
     indices = (ctypes.c_uint64 * max(1, len(wrt)))(*wrt)
@@ -338,8 +366,7 @@ def _derive_grad(program, wrt, keep_value):
         return lib.accy_b200_wire_grad(src, length, indices, len(wrt), 1 if keep_value else 0, out, capacity, n,
                                        err, err_capacity)
     wire = _transformed(call, program)
-    outputs = ([program.output_types[0]] if keep_value else []) + [program.input_types[i] for i in wrt]
-    return Program(program.name, wire, list(program.input_types), outputs)
+    return Program(program.name, wire, *_io_types(wire))
 
 
 def _derive_vmap(program, axis_size, in_axes, out_axis, axis_name):
@@ -350,21 +377,7 @@ def _derive_vmap(program, axis_size, in_axes, out_axis, axis_name):
         return lib.accy_b200_wire_vmap(src, length, int(axis_size), c_axes, len(axes), int(out_axis),
                                        axis_name.encode(), out, capacity, n, err, err_capacity)
     wire = _transformed(call, program)
-    name = axis_name
-    if not name:
-        taken = {d for t in program.input_types + program.output_types for d, _ in t.dims}
-        name, attempt = "#batch", 0
-        while name in taken:
-            attempt += 1
-            name = "#batch%d" % attempt
-
-    def widened(ty, at):
-        dims = list(ty.dims)
-        dims.insert(at, (name, int(axis_size)))
-        return Type(ty.dtype, dims)
-    inputs = [t if a < 0 else widened(t, a) for t, a in zip(program.input_types, axes)]
-    outputs = [widened(t, int(out_axis)) for t in program.output_types]
-    return Program(program.name, wire, inputs, outputs)
+    return Program(program.name, wire, *_io_types(wire))
 
 
 def define(name, specs, body):

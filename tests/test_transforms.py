@@ -343,6 +343,26 @@ def test_jvp_of_a_program_with_several_array_outputs():
     assert info.value.name == "ParameterOutOfRange"
 
 
+def test_transformations_compose():
+    """Derived programs are ordinary programs: the gradient of a gradient, the jvp of a gradient
+    (a Hessian-vector product) and the vmap of that."""
+    one = tensor.define("mismatch", [T.spec("f64"), T.spec("f64", point=16), T.spec("f64", point=16)], mismatch)
+    time = 0.25 * np.arange(16)
+    sample = np.sin(3.0 * time)
+    first = one.grad([0])
+    slope = lambda f: scalar(oracle.run(first.wire, [np.float64(f), time, sample])[0])  # noqa: E731
+    curvature = scalar(oracle.run(first.grad([0]).wire, [np.float64(2.5), time, sample])[0])
+    assert curvature == pytest.approx((slope(2.5 + 1e-6) - slope(2.5 - 1e-6)) / 2e-6, rel=1e-7)
+    product = first.jvp([0])
+    got = oracle.run(product.wire, [np.float64(2.5), time, sample, np.float64(-2.0)])
+    assert scalar(got[0]) == pytest.approx(slope(2.5), rel=1e-14)
+    assert scalar(got[1]) == pytest.approx(-2.0 * curvature, rel=1e-13)
+    guesses = np.array([2.0, 2.5, 3.0, 3.5])
+    slopes, products = oracle.run(product.vmap(4, [0, None, None, 0]).wire, [guesses, time, sample, np.ones(4)])
+    np.testing.assert_allclose(slopes, [slope(f) for f in guesses], rtol=1e-13, atol=1e-12)
+    assert products[1] == pytest.approx(curvature, rel=1e-13)
+
+
 # ---------------------------------------------------------------------------------------------
 # vmap against one run per index
 # ---------------------------------------------------------------------------------------------

@@ -72,6 +72,7 @@ PROTOTYPES = {
     "accy_b200_builder_split": (c_u32, [c_p, c_u32, c_str, P(c_str), P(ctypes.c_int64), c_u32, P(c_u32)]),
     "accy_b200_builder_merge": (c_u32, [c_p, c_u32, P(c_str), c_u32, c_str, P(c_u32)]),
     "accy_b200_builder_broadcast": (c_u32, [c_p, c_u32, P(c_str), P(ctypes.c_int64), c_u32, P(c_u32)]),
+    "accy_b200_builder_broadcast_op": (c_u32, [c_p, c_u32, P(c_str), P(ctypes.c_int64), c_u32, P(c_u32)]),
     "accy_b200_builder_value_type": (c_u32, [c_p, c_u32, P(Descriptor)]),
     "accy_b200_builder_finish": (c_u32, [c_p, P(c_u32), c_u32, P(P(ctypes.c_uint8)), P(c_size)]),
     "accy_b200_wire_reencode": (c_u32, [c_p, c_size, c_p, c_size, P(c_size), c_p, c_size]),

@@ -1139,6 +1139,11 @@ static Program withoutEmptyFolds(const Program& p) {
       case Kind::compare: made = b.compare(static_cast<Compare>(op.sub), arg(0), arg(1)); break;
       case Kind::select: made = b.select(arg(0), arg(1), arg(2)); break;
       case Kind::broadcast_in_dim: made = b.broadcastTo(arg(0), op.result.dims, op.ints); break;
+      case Kind::broadcast:
+        // a rank-0 value repeated to the result dims: the same as broadcast_in_dim with no mapped dim
+        if (p.typeOf(op.operands[0]).rank() != 0) throw PlanError("broadcast of a value that is not rank 0 is not supported");
+        made = b.broadcastTo(arg(0), op.result.dims, {});
+        break;
       case Kind::reshape: made = b.reshapeTo(arg(0), op.result.dims); break;
       case Kind::transpose: made = b.transposeBy(arg(0), op.ints); break;
       case Kind::reduce:
@@ -1201,6 +1206,7 @@ Plan planProgram(const Program& program, const ScheduleOverrides& overrides) {
   }
   bool reorder = false;
   for (const Operation& op : program.ops) {
+    reorder |= op.kind == Kind::broadcast;
     if (op.kind != Kind::dot_general) continue;
     const size_t nb = op.lhs_batch.size(), nk = op.ints.size();
     const size_t nm = program.typeOf(op.operands[0]).rank() - nb - nk;

@@ -934,6 +934,11 @@ uint32_t accy_b200_builder_broadcast(accy_b200_builder* b, uint32_t x, const cha
   return built(b, value, [&] { return b->builder.broadcastAxes(x, dimsOf(names, extents, rank)); });
 }
 
+uint32_t accy_b200_builder_broadcast_op(accy_b200_builder* b, uint32_t x, const char* const* names,
+                                        const int64_t* extents, uint32_t rank, uint32_t* value) {
+  return built(b, value, [&] { return b->builder.broadcastOp(x, dimsOf(names, extents, rank)); });
+}
+
 uint32_t accy_b200_builder_value_type(accy_b200_builder* b, uint32_t value, accy_b200_descriptor* descriptor) {
   return built(b, nullptr, [&] {
     try {

@@ -101,7 +101,7 @@ ShardInfo analyseShardAxis(const Program& p, const std::string& axis) {
         break;
       }
       case Kind::unary: case Kind::binary: case Kind::compare: case Kind::select:
-      case Kind::broadcast_in_dim: case Kind::transpose:
+      case Kind::broadcast_in_dim: case Kind::broadcast: case Kind::transpose:
         break;
       default:
         info.reason = std::string("operation kind not shardable: ") + kindName(op.kind);
@@ -163,6 +163,7 @@ Program shardProgram(const Program& p, const std::string& axis, int64_t extent) 
       case Kind::compare: made = b.compare(static_cast<Compare>(op.sub), op.operands[0], op.operands[1]); break;
       case Kind::select: made = b.select(op.operands[0], op.operands[1], op.operands[2]); break;
       case Kind::broadcast_in_dim: made = b.broadcastTo(op.operands[0], dims, op.ints); break;
+      case Kind::broadcast: made = b.broadcastOp(op.operands[0], dims); break;
       case Kind::reshape: made = b.reshapeTo(op.operands[0], dims); break;
       case Kind::transpose: made = b.transposeBy(op.operands[0], op.ints); break;
       case Kind::reduce: made = b.reduce(op.operands[0], op.operands[1], static_cast<Reducer>(op.sub), op.ints); break;

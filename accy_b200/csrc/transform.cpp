@@ -46,6 +46,7 @@ uint32_t replayUnchanged(Builder& b, const Operation& op, const std::vector<uint
     case Kind::compare: return b.compare(static_cast<Compare>(op.sub), arg(0), arg(1));
     case Kind::select: return b.select(arg(0), arg(1), arg(2));
     case Kind::broadcast_in_dim: return b.broadcastTo(arg(0), op.result.dims, op.ints);
+    case Kind::broadcast: return b.broadcastOp(arg(0), op.result.dims);
     case Kind::reshape: return b.reshapeTo(arg(0), op.result.dims);
     case Kind::transpose: return b.transposeBy(arg(0), op.ints);
     case Kind::reduce: return b.reduce(arg(0), arg(1), static_cast<Reducer>(op.sub), op.ints);
@@ -129,6 +130,9 @@ class Reverse {
         return;
       }
       case Kind::broadcast_in_dim: return pullBroadcast(op, g);
+      case Kind::broadcast:
+        if (src_.typeOf(op.operands[0]).rank() != 0) throw TensorError("UnsupportedDerivative");
+        return give(op.operands[0], sumAll(g));
       case Kind::reshape: return give(op.operands[0], b_.reshapeTo(g, src_.typeOf(op.operands[0]).dims));
       case Kind::transpose: {
         std::vector<int64_t> inverse(op.ints.size());
@@ -484,6 +488,9 @@ class Forward {
       case Kind::broadcast_in_dim:
         if (t(0)) tan_[op.id] = b_.broadcastTo(*t(0), op.result.dims, op.ints);
         return;
+      case Kind::broadcast:
+        if (t(0)) tan_[op.id] = b_.broadcastOp(*t(0), op.result.dims);
+        return;
       case Kind::reshape:
         if (t(0)) tan_[op.id] = b_.reshapeTo(*t(0), op.result.dims);
         return;
@@ -642,6 +649,10 @@ class Vmap {
         for (int64_t a : op.ints) mapping.push_back(a + 1);
         return {b_.broadcastTo(arg(0).id, withBatch(op.result.dims), mapping), true};
       }
+      case Kind::broadcast:
+        // only a rank-0 operand can carry the new axis (batch.zig:698-722)
+        if (src_.typeOf(op.operands[0]).rank() != 0) throw TensorError("UnsupportedBatching");
+        return {b_.broadcastTo(arg(0).id, withBatch(op.result.dims), {0}), true};
       case Kind::reshape: return {b_.reshapeTo(arg(0).id, withBatch(op.result.dims)), true};
       case Kind::transpose: {
         std::vector<int64_t> perm{0};

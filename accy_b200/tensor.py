@@ -241,6 +241,11 @@ class Value:
         names, extents, rank = _names_extents(list(added.items()))
         return self.builder._emit(lib.accy_b200_builder_broadcast, self.id, names, extents, rank)
 
+    def broadcast_op(self, **dims):
+        """Builder.broadcastOp (builder.zig:487-497): this rank-0 value repeated to `dims`."""
+        names, extents, rank = _names_extents(list(dims.items()))
+        return self.builder._emit(lib.accy_b200_builder_broadcast_op, self.id, names, extents, rank)
+
     def _un(self, op):
         return self.builder._emit(lib.accy_b200_builder_unary, UNARY.index(op), self.id)
 

@@ -178,6 +178,11 @@ uint32_t accy_b200_builder_merge(accy_b200_builder* b, uint32_t x, const char* c
                                  const char* merged, uint32_t* value);
 uint32_t accy_b200_builder_broadcast(accy_b200_builder* b, uint32_t x, const char* const* names,
                                      const int64_t* extents, uint32_t rank, uint32_t* value);
+/* Builder.broadcastOp (builder.zig:487-497): the `broadcast` operation, a rank-0 value repeated to
+ * the given dims (the target runs it for rank-0 operands, which is what the reference's own
+ * transformations give it, batch.zig:698-722). */
+uint32_t accy_b200_builder_broadcast_op(accy_b200_builder* b, uint32_t x, const char* const* names,
+                                        const int64_t* extents, uint32_t rank, uint32_t* value);
 uint32_t accy_b200_builder_value_type(accy_b200_builder* b, uint32_t value, accy_b200_descriptor* descriptor);
 /* Builder.finish + wire.encode: the ACTP bytes stay valid until the builder is destroyed. */
 uint32_t accy_b200_builder_finish(accy_b200_builder* b, const uint32_t* outputs, uint32_t output_count,

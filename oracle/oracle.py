@@ -174,6 +174,13 @@ def decode(data):
             op.dims = r.dims()
             op.operands = [ref()]
             op.dtype = ops[op.operands[0]].dtype
+        elif k == "broadcast":
+            # src/tensor/trace/builder.zig:487-497: same layout as reshape; a rank-0 value repeated
+            op.dims = r.dims()
+            op.operands = [ref()]
+            op.dtype = ops[op.operands[0]].dtype
+            if ops[op.operands[0]].dims:
+                raise OracleError("unsupported: broadcast of a value that is not rank 0")
         elif k == "unary":
             op.sub = UNARY[r.u32()]
             op.operands = [ref()]
@@ -388,6 +395,9 @@ class Evaluator:
                 vals[op.id] = np.ascontiguousarray(np.broadcast_to(x.reshape(view), shape))
             elif k == "reshape":
                 vals[op.id] = np.ascontiguousarray(vals[op.operands[0]]).reshape(shape)
+            elif k == "broadcast":
+                x = vals[op.operands[0]]
+                vals[op.id] = np.full(shape, x.reshape(-1)[0], dtype=x.dtype)
             elif k == "transpose":
                 vals[op.id] = np.ascontiguousarray(np.transpose(vals[op.operands[0]], op.ints))
             elif k == "reduce":

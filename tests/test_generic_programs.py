@@ -46,6 +46,9 @@ CASES = {
     "bf16_rowsum": ([T.spec("bf16", r=128, c=512)], lambda b, a: a[0].mul(a[0]).sum("c")),
     "scalar_program": ([T.spec("f32"), T.spec("f32")], lambda b, a: a[0].div(a[1]).cos()),
     "passthrough_and_duplicate": ([T.spec("f32", n=100)], lambda b, a: [a[0], a[0].neg(), a[0]]),
+    # the `broadcast` operation (Builder.broadcastOp): a rank-0 value repeated to the dims
+    "broadcast_op": ([T.spec("f32"), T.spec("f32", r=40, c=50)],
+                     lambda b, a: a[1].mul(a[0].exp().broadcast_op(r=40, c=50)).sum("c")),
     "two_stage_reduce": ([T.spec("f32", a=50, b=70)], lambda b, a: a[0].sum("b").max("a")),
     "softmax_then_colsum": ([T.spec("f32", r=64, c=128)],
                             lambda b, a: a[0].sub(a[0].max("c")).exp().div(a[0].sub(a[0].max("c")).exp().sum("c")).sum("r")),

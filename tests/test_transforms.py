@@ -182,6 +182,11 @@ def batched_dot_loss(b, a):
     return a[0].contract(a[1], "k").mul(a[2]).sum(["b", "m", "n"])
 
 
+def broadcast_op_loss(b, a):
+    scale, x = a
+    return x.mul(scale.tanh().broadcast_op(**dict(x.ty.dims))).exp().sum("n")
+
+
 def shared_scalar_loss(b, a):
     scale, x = a
     return x.mul(scale).exp().mean("n").div(scale)
@@ -199,6 +204,7 @@ GRAD_CASES = {
     "batched_dot": (batched_dot_loss, [(("b", 2), ("m", 3), ("k", 4)), (("b", 2), ("k", 4), ("n", 5)),
                                        (("b", 2), ("m", 3), ("n", 5))], [0, 1, 2]),
     "shared_scalar": (shared_scalar_loss, [(), ("n", 40)], [0, 1]),
+    "broadcast_op": (broadcast_op_loss, [(), ("n", 21)], [0, 1]),
 }
 
 
@@ -215,7 +221,7 @@ def grad_inputs(name, shapes, dtype, seed=0):
     out = []
     for i, shape in enumerate(shapes):
         extents = tuple(dims_of(shape).values())
-        if name in ("unary_zoo", "binary_zoo") and i == 0 or name == "shared_scalar" and i == 0:
+        if name in ("unary_zoo", "binary_zoo") and i == 0 or name in ("shared_scalar", "broadcast_op") and i == 0:
             v = rng.uniform(0.5, 2.0, extents)
         else:
             v = rng.uniform(-1.5, 1.5, extents)
@@ -385,6 +391,7 @@ VMAP_CASES = {
     "unmapped_output": (lambda b, a: [a[0].mul(a[1]), a[1].exp()], [("n", 6), ("n", 6)], [0, None], 1),
     "select_and_transpose": (relu_mask_loss, [(("r", 6), ("c", 7))], [2], 0),
     "layout_vmapped": (layout_loss, [(("a", 3), ("b", 4), ("c", 5)), (("c", 5), ("a", 3))], [3, 0], 0),
+    "broadcast_op_mapped_scalar": (broadcast_op_loss, [(), ("n", 21)], [0, None], 0),
     "attention_gradient": (None, [(("token", 5), ("channel", 3))] * 3, [0, 0, None], 0),
 }
 VMAP_EXTENT = 4

@@ -221,6 +221,7 @@ void oracle_softmax_layernorm_f32(const float* x, float* out, size_t rows, size_
 /* bf16 matmul oracle: f32 k-serial dot of the widened bf16 inputs, output left in f32 */
 void oracle_matmul_bf16(const uint16_t* a, const uint16_t* b, float* c, size_t m, size_t k, size_t n,
                         size_t row_begin, size_t row_end) {
+  if (row_end > m) row_end = m;
 #pragma omp parallel for schedule(static)
   for (size_t mi = row_begin; mi < row_end; ++mi) {
     for (size_t ni = 0; ni < n; ++ni) {

@@ -11,7 +11,11 @@ if ROOT not in sys.path:
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
     # build the native library and the oracle once, before collection imports them
-    from accy_b200 import build as native_build
+    # loaded by path: importing the package needs the library this builds
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("accy_b200_build", os.path.join(ROOT, "accy_b200", "build.py"))
+    native_build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(native_build)
     native_build.build()
     from oracle import build as oracle_build
     oracle_build.build()

@@ -92,7 +92,7 @@ PROTOTYPES = {
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            "accy_b200: native library %s is missing. Build it with `python -m accy_b200.build` "
+            "accy_b200: native library %s is missing. Build it with `python accy_b200/build.py` "
             "(or __graft_entry__.build()). There is no Python or CPU fallback." % LIB_PATH)
     lib = ctypes.CDLL(LIB_PATH)
     for name, (restype, argtypes) in PROTOTYPES.items():

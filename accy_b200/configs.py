@@ -155,5 +155,30 @@ def mlp(tokens=16384, d=4096, h=16384, seed=4):
     return Config("mlp", mlp_body, specs, "token", inputs, work, 2e-2, "bf16")
 
 
-BASELINE = {"mismatch": mismatch, "softmax_layernorm": softmax_layernorm, "matmul": matmul,
+class DerivedConfig(Config):
+    """A config whose program is derived from a recorded one instead of recorded directly."""
+
+    def __init__(self, derive, *args):
+        Config.__init__(self, *args)
+        self.derive = derive
+
+    def program(self):
+        return self.derive()
+
+
+def refine(guesses=8192, points=65536, seed=0):
+    """The README's gradient-descent program at the mismatch configuration's size: value and slope
+    (d/d frequency) of the one-guess mismatch, mapped over guesses:
+    define(mismatch).valueAndGrad(wrt 0).vmap(guess).  Two outputs f32[guess]."""
+    base = mismatch(guesses, points, seed)
+
+    def derive():
+        one = T.define("mismatch", [T.spec("f32"), T.spec("f32", point=points), T.spec("f32", point=points)], mismatch_body)
+        return one.value_and_grad([0]).vmap(guesses, [T.mapped_axis(0), None, None], axis_name="guess")
+    work = {"bytes": 4.0 * (guesses + 2 * points + 2 * guesses), "flops": 11.0 * guesses * points,
+            "pairs": float(guesses) * points}
+    return DerivedConfig(derive, "refine", mismatch_body, base.specs, "guess", base.make_inputs, work, 1e-5, "f32")
+
+
+BASELINE = {"refine": refine, "mismatch": mismatch, "softmax_layernorm": softmax_layernorm, "matmul": matmul,
             "attention": attention, "mlp": mlp}

@@ -103,6 +103,8 @@ WORKLOADS = {
     # name: (metric, unit, bound, quantity-per-step key, scale)
     "softmax_layernorm": ("fused_reduce_hbm_gbs", "GB/s", "hbm"),
     "mismatch": ("fused_reduce_gpairs_per_s", "Gpair/s", "hbm"),
+    # not one of the five benchmark configurations: the mismatch program's valueAndGrad + vmap
+    "refine": ("value_and_slope_gpairs_per_s", "Gpair/s", "hbm"),
     "matmul": ("matmul_tflops", "TFLOP/s", "tensor"),
     "attention": ("attention_tflops", "TFLOP/s", "tensor"),
     "mlp": ("mlp_tflops", "TFLOP/s", "tensor"),
@@ -128,7 +130,7 @@ RESIDENT_INPUTS = {"matmul": [1], "mlp": [1, 2, 3, 4, 5]}
 def _size_args(name, cfg):
     """(label, extent) pairs that rebuild a config of the same size with another seed"""
     dims = {n: e for s in cfg.specs for n, e in s.dims}
-    order = {"mismatch": ["guess", "point"], "softmax_layernorm": ["row", "col"], "matmul": ["m", "n", "k"],
+    order = {"mismatch": ["guess", "point"], "refine": ["guess", "point"], "softmax_layernorm": ["row", "col"], "matmul": ["m", "n", "k"],
              "attention": ["batch", "head", "seq", "dim"], "mlp": ["token", "d", "h"]}[name]
     return [(n, dims[n]) for n in order]
 
@@ -136,7 +138,7 @@ def _size_args(name, cfg):
 def units_per_step(name, work):
     if name == "softmax_layernorm":
         return work["bytes"] / 1e9
-    if name == "mismatch":
+    if name in ("mismatch", "refine"):
         return work["pairs"] / 1e9
     return work["flops"] / 1e12
 
@@ -144,13 +146,14 @@ def units_per_step(name, work):
 def make_config(name, args, seed_offset=0):
     from accy_b200 import configs
     if seed_offset:
-        base = {"mismatch": 0, "softmax_layernorm": 1, "matmul": 2, "attention": 3, "mlp": 4}[name]
+        base = {"mismatch": 0, "refine": 0, "softmax_layernorm": 1, "matmul": 2, "attention": 3, "mlp": 4}[name]
         sizes = make_config(name, args)
         return configs.BASELINE[name](*[e for _, e in _size_args(name, sizes)], seed=base + 1000 * seed_offset)
     if args.small:
         # profiling sizes: the same kernels, inputs still larger than L2 where the kernel is HBM-bound
         small = {"softmax_layernorm": lambda: configs.softmax_layernorm(8192, 4096),
                  "mismatch": lambda: configs.mismatch(1024, 65536),
+                 "refine": lambda: configs.refine(1024, 65536),
                  "matmul": lambda: configs.matmul(4096, 4096, 4096),
                  "attention": lambda: configs.attention(1, 16, 4096, 128),
                  "mlp": lambda: configs.mlp(4096, 4096, 4096)}
@@ -179,6 +182,16 @@ def cpu_sample(name, cfg, inputs, threads, budget_s=15.0):
 
         def run(n):
             lib.oracle_mismatch_f32(ptr(f), ptr(t), ptr(s), ptr(out), c_size(total), c_size(t.shape[0]), c_size(0), c_size(n))
+        unit_of = lambda n: n * t.shape[0] / 1e9  # noqa: E731
+        label = "guesses"
+    elif name == "refine":
+        f, t, s = inputs
+        total = f.shape[0]
+        out, slope = np.zeros(total, np.float32), np.zeros(total, np.float32)
+
+        def run(n):
+            lib.oracle_mismatch_slope_f32(ptr(f), ptr(t), ptr(s), ptr(out), ptr(slope), c_size(total), c_size(t.shape[0]),
+                                          c_size(0), c_size(n))
         unit_of = lambda n: n * t.shape[0] / 1e9  # noqa: E731
         label = "guesses"
     elif name == "softmax_layernorm":
@@ -454,6 +467,9 @@ def main():
                     "peak_source": peaks["source"], "peak_sustained": peaks["bf16_tflops_sustained"] if bound == "tensor" else None,
                     "kernel_ms": avg_ms,
                     "launches_per_step": work["launches"]}
+        if name == "refine":
+            roofline["note"] = "not HBM-bound by construction: FP32-bound (a sine, a cosine and nine more operations per pair)"
+            roofline["pairs_per_s"] = cfg.work["pairs"] / (avg_ms / 1e3)
         if name == "mismatch":
             # 0.59 MB of traffic for 5.4e8 (guess, point) pairs: the HBM fraction is reported because the
             # contract asks for it, the kernel is bound by FP32 arithmetic (ncu: FMA pipe 71 % busy,

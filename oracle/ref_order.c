@@ -174,6 +174,32 @@ void oracle_mismatch_f32(const float* frequency, const float* time, const float*
   }
 }
 
+/* value and slope of the mismatch with respect to the frequency, per guess: the program that
+ * valueAndGrad(wrt frequency) followed by vmap over guesses records (README.md:247-293).  Two fused
+ * reductions over the same elementwise chain, each a serial fold (reduction.zig:839-863); the
+ * cotangent of the squared gap is gap*1 + 1*gap, then times cos(phase), then times time[p]. */
+void oracle_mismatch_slope_f32(const float* frequency, const float* time, const float* sample, float* value,
+                               float* slope, size_t guesses, size_t points, size_t row_begin, size_t row_end) {
+  if (row_end > guesses) row_end = guesses;
+#pragma omp parallel for schedule(static)
+  for (size_t g = row_begin; g < row_end; ++g) {
+    const float f = frequency[g];
+    float acc = 0.0f, dacc = 0.0f;
+    for (size_t p = 0; p < points; ++p) {
+      float phase = f * time[p];
+      float d = sinf(phase) - sample[p];
+      float sq = d * d;
+      acc = acc + sq;
+      float twice = d + d;
+      float through_sin = twice * cosf(phase);
+      float term = through_sin * time[p];
+      dacc = dacc + term;
+    }
+    value[g] = acc;
+    slope[g] = dacc;
+  }
+}
+
 void oracle_mismatch_f64(const float* frequency, const float* time, const float* sample, double* out,
                          size_t guesses, size_t points) {
   for (size_t g = 0; g < guesses; ++g) {

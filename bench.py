@@ -295,6 +295,9 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures only; not a bench value)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--strong", action="store_true",
+                    help="with --gpus N > 1: cut the one-GPU problem into N pieces (strong scaling) instead of running "
+                         "an N times larger problem (weak scaling, the default)")
     ap.add_argument("--tpr", type=int, default=0, help="schedule override: threads per row (experiments)")
     ap.add_argument("--vpt", type=int, default=0, help="schedule override: vectors per thread (experiments)")
     ap.add_argument("--attn-poly", type=int, default=0, help="attention_poly override (experiments)")
@@ -329,11 +332,22 @@ def main():
         # its own block of the global input (a different seed per rank).
         from accy_b200 import configs, shard
         sizes = dict(_size_args(name, cfg))
-        sizes[cfg.shard_axis] *= world
-        global_cfg = configs.BASELINE[name](*[sizes[n] for n, _ in _size_args(name, cfg)])
+        if args.strong:
+            # strong scaling: the one-GPU problem itself is cut into `world` pieces
+            if sizes[cfg.shard_axis] % world:
+                raise SystemExit("--strong: axis %s of extent %d does not divide over %d ranks" % (cfg.shard_axis, sizes[cfg.shard_axis], world))
+            global_cfg = cfg
+        else:
+            sizes[cfg.shard_axis] *= world
+            global_cfg = configs.BASELINE[name](*[sizes[n] for n, _ in _size_args(name, cfg)])
         plan = shard.ShardPlan(global_cfg.program(), cfg.shard_axis, world)
         assert not plan.partial_sum
-        cfg = make_config(name, args, seed_offset=rank)
+        if args.strong:
+            sizes[cfg.shard_axis] //= world
+            base = {"mismatch": 0, "refine": 0, "softmax_layernorm": 1, "matmul": 2, "attention": 3, "mlp": 4}[name]
+            cfg = configs.BASELINE[name](*[sizes[n] for n, _ in _size_args(name, cfg)], seed=base + 1000 * rank)
+        else:
+            cfg = make_config(name, args, seed_offset=rank)
         program = plan.piece
     else:
         program = cfg.program()
@@ -482,7 +496,7 @@ def main():
             cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample}
         line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic",
+                "scaling": "strong" if (args.strong and world > 1) else "weak", "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic",
                 "config": {"workload": name, "specs": [repr(t) for t in program.input_types],
                            "shard_axis": cfg.shard_axis, "parallelism": "shard%d" % world,
                            "l2": "flushed between steps" if flush is not None else "inputs larger than L2",

@@ -502,7 +502,8 @@ def main():
                            "l2": "flushed between steps" if flush is not None else "inputs larger than L2",
                            "small": bool(args.small), "plan": compiled.plan_summary().strip().split("\n")},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": work["launches"] * args.steps,
-                "clocks": clocks, "wall_ms_per_step": 1e3 * wall / args.steps}
+                "clocks": clocks, "wall_ms_per_step": 1e3 * wall / args.steps,
+                "ms_min": float(min(step_ms)), "ms_median": float(np.median(step_ms))}
         print(json.dumps(line))
     session.deinit()
     if world > 1:

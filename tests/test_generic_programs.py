@@ -21,6 +21,10 @@ def value_and_slope(b, a):
     return [value, slope]
 
 
+def sine_and_cosine(x):
+    return [x.sin(), x.cos()]
+
+
 def masked_fill(b, a):
     x = a[0]
     dims = x.ty.dims
@@ -49,6 +53,8 @@ CASES = {
     # the `broadcast` operation (Builder.broadcastOp): a rank-0 value repeated to the dims
     "broadcast_op": ([T.spec("f32"), T.spec("f32", r=40, c=50)],
                      lambda b, a: a[1].mul(a[0].exp().broadcast_op(r=40, c=50)).sum("c")),
+    # a sine and a cosine of the same value: the joint routine, both results stored
+    "sine_and_cosine": ([T.spec("f32", n=4096)], lambda b, a: sine_and_cosine(a[0].mul(b.scalar("f32", 40.0)))),
     "two_stage_reduce": ([T.spec("f32", a=50, b=70)], lambda b, a: a[0].sum("b").max("a")),
     "softmax_then_colsum": ([T.spec("f32", r=64, c=128)],
                             lambda b, a: a[0].sub(a[0].max("c")).exp().div(a[0].sub(a[0].max("c")).exp().sum("c")).sum("r")),

@@ -376,3 +376,40 @@ def test_chunked_host_invoke_equals_single_shot(make):
         results.append(outs[0].copy())
         session.deinit()
     assert np.array_equal(results[0], results[1])
+
+
+def _ulps(got, want64):
+    want32 = want64.astype(np.float32)
+    return np.abs(got.astype(np.float64) - want64) / np.abs(np.spacing(want32)).astype(np.float64)
+
+
+def test_packed_sine_and_cosine_are_accurate_to_two_ulp(gpu_session):
+    """The row kernels' own sine / cosine (packed FP32, no library call): each alone, and the joint
+    routine used when a program takes both of the same value.  Against f64 over |x| <= 1e5, near
+    multiples of pi/2, on the mismatch configuration's phases, and beyond 1e5 (where the thread
+    falls back to sinf / cosf); infinities give NaN and NaN stays NaN."""
+    rng = np.random.default_rng(31)
+    n = 1 << 20
+    parts = [rng.uniform(-100.0, 100.0, n // 4), rng.uniform(-1e5, 1e5, n // 4),
+             np.pi / 2 * rng.integers(-63000, 63000, n // 4) + rng.uniform(-1e-3, 1e-3, n // 4),
+             rng.uniform(0.0, 6.0, n // 4).astype(np.float32) * (0.25 * rng.integers(0, 65536, n // 4)).astype(np.float32)]
+    x = np.concatenate(parts).astype(np.float32)
+    x[:8] = [0.0, -0.0, 3.0e5, -7.5e6, np.inf, -np.inf, np.nan, 1.0e5]
+    x64 = x.astype(np.float64)
+    finite = np.isfinite(x)
+    spec = [tensor.spec("f32", n=n)]
+    programs = {"sine": lambda b, a: a[0].sin(), "cosine": lambda b, a: a[0].cos(),
+                "both": lambda b, a: [a[0].sin(), a[0].cos()]}
+    for name, body in programs.items():
+        program = tensor.define("packed_" + name, spec, body)
+        compiled = gpu_session.compile(program)
+        assert ("w0 ?" in compiled.kernels()[0][1]) == (name == "both")   # the joint routine only where both are asked for
+        outs = [np.empty(n, np.float32) for _ in program.output_types]
+        gpu_session.invoke(compiled, [x], outs)
+        gpu_session.release(compiled)
+        wants = {"sine": [np.sin], "cosine": [np.cos], "both": [np.sin, np.cos]}[name]
+        for got, fn in zip(outs, wants):
+            with np.errstate(invalid="ignore"):
+                want = fn(x64)
+            assert np.all(np.isnan(got[~finite]))
+            assert _ulps(got[finite], want[finite]).max() < 2.0, name

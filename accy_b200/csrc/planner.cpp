@@ -208,7 +208,17 @@ class Planner {
     std::set<uint32_t> closure;        // computed values inlined into this region
   };
 
+  // Nodes are pure functions of their arguments: one that repeats an earlier node (the same
+  // subexpression recorded twice, e.g. x.sub(x.max(c)) written out for two uses) is that node.
   int addNode(Build& b, const ENode& n) {
+    if (n.op != ENode::Leaf) {
+      for (size_t i = 0; i < b.nodes.size(); ++i) {
+        const ENode& e = b.nodes[i];
+        if (e.op == n.op && e.sub == n.sub && e.dtype == n.dtype && e.args[0] == n.args[0] && e.args[1] == n.args[1] &&
+            e.args[2] == n.args[2] && e.bits == n.bits && e.dim == n.dim && e.vary == n.vary && e.level == n.level)
+          return static_cast<int>(i);
+      }
+    }
     b.nodes.push_back(n);
     return static_cast<int>(b.nodes.size()) - 1;
   }

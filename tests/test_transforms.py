@@ -81,6 +81,23 @@ def test_refine_eight_frequency_guesses_with_the_oracle():
     check_descent(*descend(lambda f: oracle.run(each.wire, [f, time, sample])))
 
 
+def test_c_restatement_of_the_refine_program_equals_its_evaluation():
+    """bench.py's CPU leg for `--workload refine` runs oracle_mismatch_slope_f32 (oracle/ref_order.c);
+    it must be the derived program's own arithmetic in the reference's order: bit for bit what the
+    oracle's evaluator gives for valueAndGrad + vmap of the recorded mismatch."""
+    import ctypes
+    from accy_b200 import configs
+    cfg = configs.refine(6, 256)
+    inputs = cfg.make_inputs()
+    want_value, want_slope = oracle.run(cfg.program().wire, inputs)
+    value, slope = np.zeros(6, np.float32), np.zeros(6, np.float32)
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)  # noqa: E731
+    size = ctypes.c_size_t
+    oracle.lib().oracle_mismatch_slope_f32(ptr(inputs[0]), ptr(inputs[1]), ptr(inputs[2]), ptr(value), ptr(slope),
+                                           size(6), size(256), size(0), size(6))
+    assert np.array_equal(value, want_value) and np.array_equal(slope, want_slope)
+
+
 def test_function_keeps_its_derived_programs():
     """src/tensor/function.zig: derived functions hang off the root, whatever they were derived from."""
     f = tensor.Function.define("mismatch", [T.spec("f32"), T.spec("f32", point=16), T.spec("f32", point=16)], mismatch)

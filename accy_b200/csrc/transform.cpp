@@ -29,6 +29,14 @@ uint32_t filled(Builder& b, const Type& ty, double v) {
   return b.broadcastTo(scalar, ty.dims, {});
 }
 
+// Zeros of any element type (an output that carries no derivative, e.g. an integer mask).
+uint32_t zerosOf(Builder& b, const Type& ty) {
+  std::vector<uint8_t> payload(dtypeSize(ty.dtype), 0);
+  uint32_t scalar = b.constantBytes(Type{ty.dtype, {}}, payload.data(), payload.size());
+  if (ty.rank() == 0) return scalar;
+  return b.broadcastTo(scalar, ty.dims, {});
+}
+
 // Same value, dims relabelled to `dims` (same extents) when the names differ.
 uint32_t relabel(Builder& b, uint32_t x, const std::vector<Dim>& dims) {
   if (sameDims(b.typeOf(x).dims, dims)) return x;
@@ -395,7 +403,7 @@ class Forward {
   }
 
   uint32_t primal(uint32_t id) const { return now_[id]; }
-  uint32_t tangent(uint32_t id) { return tan_[id] ? *tan_[id] : filled(b_, src_.typeOf(id), 0.0); }
+  uint32_t tangent(uint32_t id) { return tan_[id] ? *tan_[id] : zerosOf(b_, src_.typeOf(id)); }
 
  private:
   using Opt = std::optional<uint32_t>;
@@ -554,10 +562,7 @@ Program jvpProgram(const Program& src, const std::vector<size_t>& wrt) {
   Forward pass(src, b, wrt);
   std::vector<uint32_t> outputs;
   for (uint32_t id : src.outputs) outputs.push_back(pass.primal(id));
-  for (uint32_t id : src.outputs) {
-    if (!dtypeIsFloat(src.typeOf(id).dtype)) throw TensorError("UnsupportedDerivative");
-    outputs.push_back(pass.tangent(id));
-  }
+  for (uint32_t id : src.outputs) outputs.push_back(pass.tangent(id));  // zeros where nothing differentiable arrives
   return b.finish(outputs);
 }
 

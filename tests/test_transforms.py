@@ -361,6 +361,10 @@ def test_jvp_of_a_program_with_several_array_outputs():
         np.testing.assert_allclose(primal, plain, rtol=1e-14)
         np.testing.assert_allclose(tangent, (u - d) / (2 * h), rtol=1e-6, atol=1e-8)
     assert not outs[5].any()                  # w*w does not depend on x: its tangent is zeros
+    # an integer output has a zero tangent of its own type (autodiff.zig:222-233 emits zeros for compare / iota)
+    mask = tensor.define("mask", [T.spec("f64", n=5)], lambda b, a: [a[0].exp(), b.iota("i32", [("n", 5)], "n")])
+    primal, count, tangent, none = oracle.run(mask.jvp([0]).wire, [np.zeros(5), np.ones(5)])
+    assert tangent.tolist() == [1, 1, 1, 1, 1] and none.dtype == np.int32 and not none.any() and count.tolist() == [0, 1, 2, 3, 4]
     with pytest.raises(tensor.TensorError) as info:
         program.jvp([2])
     assert info.value.name == "ParameterOutOfRange"

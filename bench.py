@@ -486,9 +486,9 @@ def main():
             roofline["pairs_per_s"] = cfg.work["pairs"] / (avg_ms / 1e3)
         if name == "mismatch":
             # 0.59 MB of traffic for 5.4e8 (guess, point) pairs: the HBM fraction is reported because the
-            # contract asks for it, the kernel is bound by FP32 arithmetic (ncu: FMA pipe 71 % busy,
-            # 13.85 instructions per pair; profiles/row_kernel_mismatch.md)
-            roofline["note"] = "not HBM-bound by construction: FP32-bound, FMA pipe 71 % busy under ncu"
+            # contract asks for it, the kernel is bound by FP32 arithmetic (ncu: FMA pipe 68 % busy,
+            # 12.85 instructions per pair; profiles/row_kernel_mismatch.md)
+            roofline["note"] = "not HBM-bound by construction: FP32-bound, FMA pipe 68 % busy under ncu"
             roofline["pairs_per_s"] = cfg.work["pairs"] / (avg_ms / 1e3)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:

@@ -19,7 +19,7 @@ class Options(ctypes.Structure):
     _fields_ = [("device", ctypes.c_int32), ("threads_per_row", ctypes.c_int32),
                 ("vectors_per_thread", ctypes.c_int32), ("column_splits", ctypes.c_int32),
                 ("force_simt_gemm", ctypes.c_int32), ("row_min_blocks", ctypes.c_int32),
-                ("single_shot_invoke", ctypes.c_int32), ("attention_poly", ctypes.c_int32)]
+                ("single_shot_invoke", ctypes.c_int32)]
 
 
 class Descriptor(ctypes.Structure):
@@ -66,6 +66,7 @@ PROTOTYPES = {
     "accy_b200_builder_compare": (c_u32, [c_p, c_u32, c_u32, c_u32, P(c_u32)]),
     "accy_b200_builder_select": (c_u32, [c_p, c_u32, c_u32, c_u32, P(c_u32)]),
     "accy_b200_builder_reduce": (c_u32, [c_p, c_u32, c_u32, P(c_str), c_u32, P(c_u32)]),
+    "accy_b200_builder_reduce_with": (c_u32, [c_p, c_u32, c_u32, c_u32, P(c_str), c_u32, P(c_u32)]),
     "accy_b200_builder_mean": (c_u32, [c_p, c_u32, P(c_str), c_u32, P(c_u32)]),
     "accy_b200_builder_contract": (c_u32, [c_p, c_u32, c_u32, P(c_str), c_u32, P(c_u32)]),
     "accy_b200_builder_rename": (c_u32, [c_p, c_u32, c_str, c_str, P(c_u32)]),
@@ -83,8 +84,10 @@ PROTOTYPES = {
                             P(c_size), c_p, c_size]),
     "accy_b200_wire_describe": (c_u32, [c_p, c_size, c_p, c_size, P(c_size)]),
     "accy_b200_mismatch_noalloc": (c_u32, [c_p, c_p, c_p, c_p, c_u64, c_u64, c_u32, c_p, c_p, c_size]),
+    "accy_b200_probe_fp32_rates": (c_u32, [c_p, P(ctypes.c_double), P(ctypes.c_double), c_p, c_size]),
     "accy_b200_test_use_fake_driver": (None, [ctypes.c_int32]),
     "accy_b200_test_fake_fail": (None, [c_str, ctypes.c_int32]),
+    "accy_b200_test_fake_device_status": (None, [ctypes.c_int32]),
     "accy_b200_test_fake_call_count": (c_u32, [c_str]),
 }
 

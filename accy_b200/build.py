@@ -1,9 +1,12 @@
-"""Builds libaccy_b200.so (C++17 host library behind the C ABI) in-tree with g++.
+"""Builds libaccy_b200.so (C++17 host library behind the C ABI) in-tree with g++ and nvcc.
 
-The library links neither libcuda nor libnvrtc (both are dlopen'ed at run time), so it builds and
-loads on machines without a GPU.  Kernels are CUDA templates the library instantiates per program
-and compiles for sm_100a through NVRTC; `check_kernels_with_nvcc` cross-compiles the same sources
-with nvcc to prove they build and to record registers/spills/shared memory (-Xptxas -v).
+Needs the CUDA toolkit (nvcc and libcudart_static.a under $CUDA_HOME, default /usr/local/cuda):
+the fixed-function kernels of CU_SOURCES are compiled ahead of time for sm_100a and linked with
+the static CUDA runtime.  No GPU is needed to build or to load the library: libcuda and libnvrtc
+are dlopen'ed at run time, and the static runtime touches no device until one of its entry points
+is called.  All other kernels are CUDA templates the library instantiates per program and compiles
+for sm_100a through NVRTC; `check_kernels_with_nvcc` cross-compiles the same sources with nvcc to
+prove they build and to record registers/spills/shared memory (-Xptxas -v).
 """
 import os
 import subprocess
@@ -27,16 +30,19 @@ def needs_build():
 
 
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
-CU_SOURCES = ["noalloc.cu"]   # fixed-function kernels compiled ahead of time by nvcc for sm_100a
+CU_SOURCES = ["noalloc.cu", "probe.cu"]   # fixed-function kernels compiled ahead of time by nvcc for sm_100a
 
 
 def build(force=False, verbose=False):
     if not force and not needs_build():
         return LIB
     objects = []
+    nvcc = os.path.join(CUDA_HOME, "bin", "nvcc")
+    if not os.path.exists(nvcc):
+        raise RuntimeError("building libaccy_b200.so needs the CUDA toolkit: %s not found (set CUDA_HOME)" % nvcc)
     for cu in CU_SOURCES:
         obj = os.path.join(HERE, cu.replace(".cu", ".o"))
-        cmd = [os.path.join(CUDA_HOME, "bin", "nvcc"), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
+        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
                "-std=c++17", "-Xcompiler", "-fPIC", "-c", os.path.join(CSRC, cu), "-o", obj]
         if verbose:
             print(" ".join(cmd))

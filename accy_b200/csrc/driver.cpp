@@ -21,6 +21,7 @@ bool g_real_loaded = false;
 DriverTable g_real{};
 std::map<std::string, unsigned> g_fake_calls;
 std::map<std::string, int> g_fake_fail;  // function -> remaining successful calls before failing
+int g_fake_device_status = 0;            // what the next 4-byte device-to-host reads deliver (0 = the memory's own bytes)
 
 template <typename F>
 void bind(void* lib, F& slot, const char* symbol) {
@@ -116,6 +117,9 @@ CUresult_t f_cuMemcpyHtoDAsync(CUdeviceptr_t d, const void* s, size_t n, CUstrea
 CUresult_t f_cuMemcpyDtoHAsync(void* d, CUdeviceptr_t s, size_t n, CUstream_t) {
   CUresult_t r = fakeResult("cuMemcpyDtoHAsync");
   if (!r) std::memcpy(d, reinterpret_cast<void*>(s), n);
+  // a kernel that gave up on a bounded wait leaves a code in the session's status word, which the
+  // host reads back as one int: the fake delivers the injected code for such reads
+  if (!r && n == sizeof(int) && g_fake_device_status != 0) std::memcpy(d, &g_fake_device_status, n);
   return r;
 }
 CUresult_t f_cuMemsetD8Async(CUdeviceptr_t d, unsigned char v, size_t n, CUstream_t) {
@@ -219,6 +223,12 @@ void useFakeDriver(bool enable) {
   g_use_fake = enable;
   g_fake_calls.clear();
   g_fake_fail.clear();
+  g_fake_device_status = 0;
+}
+
+void fakeDeviceStatus(int value) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_fake_device_status = value;
 }
 
 void fakeFailAfter(const std::string& function, int calls) {

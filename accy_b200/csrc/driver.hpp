@@ -77,6 +77,7 @@ const DriverTable& driver();
 void useFakeDriver(bool enable);
 void fakeFailAfter(const std::string& function, int calls);
 unsigned fakeCallCount(const std::string& function);
+void fakeDeviceStatus(int value);   // the code later reads of the device status word return (0 = none)
 std::string driverErrorName(CUresult_t r);
 
 // NVRTC: CUDA source -> sm_100a cubin.  Throws std::runtime_error carrying the compiler log.

@@ -33,7 +33,6 @@ namespace accy {
 
 extern const char* kConvertPrelude;
 extern const char* kTcPreludeShared;
-bool attentionReady() { return true; }
 
 namespace {
 
@@ -60,10 +59,8 @@ const char* kAttentionHead = R"CUDA(
 #define N_ITEMS (N_PAIRS * BATCH)
 #define SCALE_LOG2 @SCALE_LOG2@f
 #define RESCALE_THRESHOLD 8.0f
-#define POLY_SHARE @POLY_SHARE@   // of every 8 pairs in the odd 32-column quarters
 #define AB_FORMAT @AB_FORMAT@   // operand format of the MMAs: 0 = f16, 1 = bf16 (P is written in the same format)
 #define PACK16 @PACK16@
-#define HALF_HANDOFF @HALF_HANDOFF@   // P is handed to the MMA issuer 64 keys at a time
 #ifndef INFINITY
 #define INFINITY __int_as_float(0x7f800000)
 #endif
@@ -73,29 +70,7 @@ __device__ __forceinline__ unsigned long long pk2(float lo, float hi) { unsigned
 __device__ __forceinline__ unsigned long long pk2u(unsigned int lo, unsigned int hi) { unsigned long long r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi)); return r; }
 __device__ __forceinline__ void upk2(unsigned long long v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
 __device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) { unsigned long long r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
-__device__ __forceinline__ unsigned long long sub2(unsigned long long a, unsigned long long b) { unsigned long long r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
 __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) { unsigned long long r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
-// 2^x for a pair of values on the FMA pipe: x = n + f with n = round(x), f in [-1/2, 1/2];
-// 2^f by a degree-4 polynomial (error below 2^-14, the result is rounded to bf16 afterwards),
-// then n is added to the exponent field.  x is clamped at -126 so the exponent cannot wrap.
-__device__ __forceinline__ void poly_exp2_pair(unsigned long long x2, float& out0, float& out1) {
-  float x0, x1;
-  upk2(x2, x0, x1);
-  x2 = pk2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
-  const unsigned long long magic2 = pk2(12582912.0f, 12582912.0f);
-  const unsigned long long t2 = add2(x2, magic2);
-  const unsigned long long f2 = sub2(x2, sub2(t2, magic2));
-  unsigned long long p2 = fma2(f2, pk2(0.00961813f, 0.00961813f), pk2(0.05550411f, 0.05550411f));
-  p2 = fma2(p2, f2, pk2(0.24022651f, 0.24022651f));
-  p2 = fma2(p2, f2, pk2(0.69314718f, 0.69314718f));
-  p2 = fma2(p2, f2, pk2(1.0f, 1.0f));
-  float p0, p1, t0, t1;
-  upk2(p2, p0, p1);
-  upk2(t2, t0, t1);
-  out0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-  out1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
-}
-
 // three-input max (one instruction on sm_100) where the compiler's PTX version has it
 #if __CUDACC_VER_MAJOR__ > 12 || (__CUDACC_VER_MAJOR__ == 12 && __CUDACC_VER_MINOR__ >= 9)
 __device__ __forceinline__ float max3(float a, float b, float c) { float r; asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c)); return r; }
@@ -322,14 +297,12 @@ const char* kAttentionIssuer = R"CUDA(
           const bool more = j + 1 < n_t;
           // the operands first (they are normally long in place), then P, then the turn
           if (!wait_block(B_V_FULL, g) || (more && !wait_block(B_K_FULL, g + 1))) { ok = false; break; }
-          if (!mbar_wait(BAR((HALF_HANDOFF ? B_P_HALF : B_P_FULL) + t), ph, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(BAR(B_P_HALF + t), ph, abort_flag)) { ok = false; break; }
           if (!wait_turn(my_turn)) { ok = false; break; }
           tc_fence_after();
           issue_pv_part(g, 0, j == 0);
-          if (HALF_HANDOFF) {
-            if (!mbar_wait(BAR(B_P_FULL + t), ph, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-          }
+          if (!mbar_wait(BAR(B_P_FULL + t), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
           issue_pv_part(g, TILE / 32, j == 0);
           // The next S goes out before this step's other commits: the tile's softmax waits for
           // it, nothing waits as urgently for "O is up to date" or for the free V stage (a
@@ -458,34 +431,29 @@ const char* kAttentionSoftmax = R"CUDA(
           }
         }
         // p = 2^(scale * s - m) as packed FMAs and ex2, packed row sums, bf16 pairs written over S
-        // 64 keys at a time.  A fixed share of the exponentials (POLY_SHARE of every 8 pairs of
-        // the odd quarters) can run on the FMA pipe instead of the special-function unit.
+        // 64 keys at a time (the first half of P V starts while the second half's exponentials run).
         const unsigned long long c2 = pk2(SCALE_LOG2, SCALE_LOG2);
         unsigned long long nm2 = pk2(-m_run, -m_run);
         unsigned long long l2a = pk2(0.0f, 0.0f), l2b = l2a;
-#define EXP_QUARTER(R, COL0, OUT, AT, ACC, MASKED, POLY)                                     \
+#define EXP_QUARTER(R, COL0, OUT, AT, ACC, MASKED)                                           \
         _Pragma("unroll")                                                                    \
         for (int i = 0; i < 32; i += 2) {                                                    \
           const unsigned long long x2 = fma2(pk2u(R[i], R[i + 1]), c2, nm2);                 \
           float p0, p1;                                                                      \
-          if (!(MASKED) && (POLY) && ((i >> 1) & 7) < POLY_SHARE) {                          \
-            poly_exp2_pair(x2, p0, p1);                                                      \
-          } else {                                                                           \
-            upk2(x2, p0, p1);                                                                \
-            if (MASKED) {                                                                    \
-              if ((COL0) + i > lim) p0 = -INFINITY;                                          \
-              if ((COL0) + i + 1 > lim) p1 = -INFINITY;                                      \
-            }                                                                                \
-            p0 = fast_exp2(p0);                                                              \
-            p1 = fast_exp2(p1);                                                              \
+          upk2(x2, p0, p1);                                                                  \
+          if (MASKED) {                                                                      \
+            if ((COL0) + i > lim) p0 = -INFINITY;                                            \
+            if ((COL0) + i + 1 > lim) p1 = -INFINITY;                                        \
           }                                                                                  \
+          p0 = fast_exp2(p0);                                                                \
+          p1 = fast_exp2(p1);                                                                \
           ACC = add2(ACC, pk2(p0, p1));                                                      \
-          OUT[(AT) + (i >> 1)] = PACK16(p0, p1);                                          \
+          OUT[(AT) + (i >> 1)] = PACK16(p0, p1);                                             \
         }
         // The second half's arithmetic takes a word read after the arrival (always zero) as an
         // input, so that it cannot be scheduled ahead of the first half's store and arrival.
 #define HALF_READY()                                                                         \
-        if (HALF_HANDOFF) {                                                                  \
+        {                                                                                    \
           tc_wait_st();                                                                      \
           tc_fence_before();                                                                 \
           __syncwarp();                                                                      \
@@ -496,20 +464,20 @@ const char* kAttentionSoftmax = R"CUDA(
         {
           unsigned int pa[32], pb[32];
           if (diagonal) {
-            EXP_QUARTER(r0, 0, pa, 0, l2a, true, false)
-            EXP_QUARTER(r1, 32, pa, 16, l2b, true, false)
+            EXP_QUARTER(r0, 0, pa, 0, l2a, true)
+            EXP_QUARTER(r1, 32, pa, 16, l2b, true)
             tc_st32(s_addr, pa);
             HALF_READY()
-            EXP_QUARTER(r2, 64, pb, 0, l2a, true, false)
-            EXP_QUARTER(r3, 96, pb, 16, l2b, true, false)
+            EXP_QUARTER(r2, 64, pb, 0, l2a, true)
+            EXP_QUARTER(r3, 96, pb, 16, l2b, true)
             tc_st32(s_addr + 32, pb);
           } else {
-            EXP_QUARTER(r0, 0, pa, 0, l2a, false, false)
-            EXP_QUARTER(r1, 32, pa, 16, l2b, false, true)
+            EXP_QUARTER(r0, 0, pa, 0, l2a, false)
+            EXP_QUARTER(r1, 32, pa, 16, l2b, false)
             tc_st32(s_addr, pa);
             HALF_READY()
-            EXP_QUARTER(r2, 64, pb, 0, l2a, false, false)
-            EXP_QUARTER(r3, 96, pb, 16, l2b, false, true)
+            EXP_QUARTER(r2, 64, pb, 0, l2a, false)
+            EXP_QUARTER(r3, 96, pb, 16, l2b, false)
             tc_st32(s_addr + 32, pb);
           }
         }
@@ -601,14 +569,6 @@ void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan, co
   replaceAll(src, "@BATCH@", std::to_string(a.batch));
   replaceAll(src, "@CAUSAL@", a.causal ? "1" : "0");
   replaceAll(src, "@SCALE_LOG2@", scale.str());
-  // Share of exponentials moved to the FMA pipe: 0/8, 2/8, 4/8 or 8/8 of the pairs of the odd
-  // quarters, i.e. none, 1/8, 1/4 or 1/2 of all elements.  Measured on the causal 4096 x 128
-  // benchmark every share above none was slower (the extra instructions compete with the MMA
-  // issuers for issue slots), so the automatic choice is none.
-  const int poly_code = ov.attention_poly & 7;
-  const int poly_share = poly_code == 2 ? 2 : poly_code == 3 ? 4 : poly_code == 4 ? 8 : 0;
-  replaceAll(src, "@POLY_SHARE@", std::to_string(poly_share));
-  replaceAll(src, "@HALF_HANDOFF@", (ov.attention_poly & 8) ? "0" : "1");
   replaceAll(src, "@AB_FORMAT@", a.dtype == DType::f16 ? "0u" : "1u");
   replaceAll(src, "@PACK16@", a.dtype == DType::f16 ? "pack_f16" : "pack_bf16");
   KernelSource ks;

@@ -24,7 +24,6 @@ std::string emitEpilogueBody(const Epilogue& ep, std::ostringstream& o, const st
 std::string epilogueParams(const Epilogue& ep);
 extern const char* kConvertPrelude;
 
-bool tcgen05Ready() { return true; }
 
 namespace {
 

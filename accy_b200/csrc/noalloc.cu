@@ -143,10 +143,20 @@ extern "C" uint32_t accy_b200_mismatch_noalloc(const float* frequency, const flo
   }
   cudaStream_t on = static_cast<cudaStream_t>(stream);
   dim3 grid((unsigned)guesses, splits);
+  // An error the caller's own runtime calls left pending on this thread is not this call's: it is
+  // handed back as such (and thereby cleared) before anything is launched.
+  cudaError_t rc = cudaGetLastError();
+  if (rc != cudaSuccess) {
+    char text[200];
+    snprintf(text, sizeof(text), "an earlier CUDA error was pending on this thread, nothing launched: %s", cudaGetErrorString(rc));
+    return fail(error, error_capacity, ACCY_B200_LAUNCH_FAILED, text);
+  }
   mismatch_partials<<<grid, kThreads, 0, on>>>(frequency, time, sample, partials, (long long)points,
                                                 chunks_per_split, (int)splits);
+  rc = cudaGetLastError();
+  if (rc != cudaSuccess) return fail(error, error_capacity, ACCY_B200_LAUNCH_FAILED, cudaGetErrorString(rc));
   mismatch_combine<<<(unsigned)((guesses + 127) / 128), 128, 0, on>>>(partials, out, (long long)guesses, (int)splits);
-  cudaError_t rc = cudaGetLastError();
+  rc = cudaGetLastError();
   if (rc != cudaSuccess) return fail(error, error_capacity, ACCY_B200_LAUNCH_FAILED, cudaGetErrorString(rc));
   return ACCY_B200_OK;
 }

@@ -151,7 +151,6 @@ struct ScheduleOverrides {
   int column_splits = 0;
   int force_simt_gemm = 0;
   int row_min_blocks = 0;
-  int attention_poly = 0;        // low 3 bits: 0 automatic, 1 none, 2 = 1/8, 3 = 1/4, 4 = 1/2 of the exponentials by polynomial; +8: P handed over in one piece
   int sm_count = 148;
 };
 
@@ -200,8 +199,6 @@ void emitRowKernels(const Cluster& c, const RowSchedule& s, const std::string& n
 void emitGemm(const GemmOp& g, const std::string& name, Plan& plan, const ScheduleOverrides& o);
 void emitAttention(const AttentionOp& a, const std::string& name, Plan& plan,
                    const ScheduleOverrides& o);
-bool tcgen05Ready();
-bool attentionReady();
 // Emits the C expression that evaluates an elementwise node from its operand expressions.
 std::string elementwiseExpr(const ENode& n, const std::string& a, const std::string& b,
                             const std::string& c, DType a_dtype);

@@ -866,7 +866,7 @@ class Planner {
     const bool aligned = g.m >= 128 && g.n >= 128 && g.k >= 64 && g.k % 8 == 0 && a_ok &&
                          ((g.b_stride_n == 1 && g.n % 8 == 0) || g.b_stride_k == 1);
     const bool half_inputs = (g.in_dtype == DType::bf16 && g.b_dtype == DType::bf16) || (g.in_dtype == DType::f16 && g.b_dtype == DType::f16);
-    g.tensor_core = half_inputs && aligned && !ov.force_simt_gemm && tcgen05Ready();
+    g.tensor_core = half_inputs && aligned && !ov.force_simt_gemm;
     std::string name = nextName(g.tensor_core ? "gemm_tc" : "gemm_simt");
     summary << "gemm: " << name << " batch=" << g.batch << " m=" << g.m << " n=" << g.n << " k=" << g.k
             << " in=" << dtypeName(g.in_dtype) << " out=" << dtypeName(g.out_dtype)
@@ -1001,6 +1001,12 @@ class Planner {
     if (sum.kind != Kind::reduce || sum.sub != static_cast<uint8_t>(Reducer::sum) || sum.operands[0] != e_id ||
         sum.ints.size() != 1 || sum.ints[0] != static_cast<int64_t>(rank - 1))
       return false;
+    {
+      // the fused kernel sums from zero and takes the maximum from -inf: other recorded initial
+      // values leave the pattern to the generic kernels, which fold them in
+      double sum_init;
+      if (!scalarConstant(sum.operands[1], &sum_init) || sum_init != 0.0) return false;
+    }
     const Operation& e = take(e_id);
     if (e.kind != Kind::unary || e.sub != static_cast<uint8_t>(Unary::exp)) return false;
     const Operation& shifted = take(e.operands[0]);
@@ -1011,6 +1017,10 @@ class Planner {
     if (mx.kind != Kind::reduce || mx.sub != static_cast<uint8_t>(Reducer::max) || mx.operands[0] != s_id ||
         mx.ints.size() != 1 || mx.ints[0] != static_cast<int64_t>(rank - 1))
       return false;
+    {
+      double max_init;
+      if (!scalarConstant(mx.operands[1], &max_init) || !(max_init < -1e30)) return false;
+    }
     // optional causal mask
     bool causal = false;
     uint32_t cur = s_id;
@@ -1103,7 +1113,7 @@ class Planner {
                                     g2.b_stride_b == a.k_len * a.head_dim));
     bool shape = (a.head_dim == 128 || a.head_dim == 64) && a.q_len >= 128 && a.k_len >= 128 && (!causal || a.q_len == a.k_len) &&
                  scale > 0.0;
-    if (!layout || !shape || ov.force_simt_gemm || !attentionReady()) return false;
+    if (!layout || !shape || ov.force_simt_gemm) return false;
     a.q_slot = g1.a_slot;
     a.k_slot = g1.b_slot;
     a.v_slot = g2.b_slot;

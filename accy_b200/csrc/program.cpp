@@ -578,6 +578,11 @@ uint32_t Builder::reduceNamed(uint32_t x, Reducer r, const std::vector<std::stri
   return reduce(x, init, r, indices);
 }
 
+uint32_t Builder::reduceWith(uint32_t x, uint32_t init, Reducer r, const std::vector<std::string>& names) {
+  ensure(x);
+  return reduce(x, init, r, axisIndices(typeOf(x).dims, names));
+}
+
 uint32_t Builder::meanNamed(uint32_t x, const std::vector<std::string>& names) {
   ensure(x);
   std::vector<int64_t> indices = axisIndices(typeOf(x).dims, names);

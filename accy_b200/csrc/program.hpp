@@ -120,6 +120,7 @@ class Builder {
   uint32_t alignedCompare(Compare dir, uint32_t lhs, uint32_t rhs);
   uint32_t alignedSelect(uint32_t pred, uint32_t on_true, uint32_t on_false);
   uint32_t reduceNamed(uint32_t x, Reducer r, const std::vector<std::string>& names);
+  uint32_t reduceWith(uint32_t x, uint32_t init, Reducer r, const std::vector<std::string>& names);
   uint32_t meanNamed(uint32_t x, const std::vector<std::string>& names);
   uint32_t contract(uint32_t lhs, uint32_t rhs, const std::vector<std::string>& names);
   uint32_t renameAxis(uint32_t x, const std::string& old_name, const std::string& new_name);

@@ -53,6 +53,14 @@ struct Entry {
   CUgraphExec_t graph = nullptr;
   std::vector<CUdeviceptr_t> graph_bound;
   int graph_recordings = 0;              // re-recordings so far; callers that change pointers every time stop being recorded
+  // Encoded tensor maps, one per (launch, argument), kept while the pointer they were encoded for
+  // stays bound: a steady invoke loop does no cuTensorMapEncodeTiled on its launch path.
+  struct CachedMap {
+    CUdeviceptr_t base = 0;
+    bool valid = false;
+    TensorMap map;
+  };
+  std::vector<std::vector<CachedMap>> map_cache;
   // Chunked host invoke: the program re-recorded for a slice of its outermost batch-like axis,
   // loaded three times (three lanes = three streams with their own buffers) so that the copy in
   // of chunk i+1, the kernels of chunk i and the copy out of chunk i-1 overlap.
@@ -142,7 +150,6 @@ struct accy_b200_session {
     ov.column_splits = options.column_splits;
     ov.force_simt_gemm = options.force_simt_gemm;
     ov.row_min_blocks = options.row_min_blocks;
-    ov.attention_poly = options.attention_poly;
     ov.sm_count = sm_count;
     x.plan = planProgram(x.program, ov);
     observe("plan", t0);
@@ -279,7 +286,8 @@ struct accy_b200_session {
       for (size_t i = 0; i < P.input_sharded.size(); ++i) {
         int slot = x.plan.input_slots[i];
         if (!P.input_sharded[i]) {
-          x.bound[slot] = inputs[i] ? P.shared_inputs[i] : e.resident[i];
+          // a zero-byte input may be NULL without ever having been made resident
+          x.bound[slot] = inputs[i] ? P.shared_inputs[i] : (i < e.resident.size() ? e.resident[i] : 0);
           continue;
         }
         size_t bytes = x.plan.slots[slot].bytes;
@@ -422,23 +430,32 @@ struct accy_b200_session {
 
   void issueLaunches(Entry& e, CUstream_t on) {
     const DriverTable& d = driver();
-    for (const Launch& l : e.plan.launches) {
+    if (e.map_cache.size() != e.plan.launches.size()) {
+      e.map_cache.clear();
+      e.map_cache.resize(e.plan.launches.size());
+      for (size_t i = 0; i < e.plan.launches.size(); ++i) e.map_cache[i].resize(e.plan.launches[i].args.size());
+    }
+    for (size_t li = 0; li < e.plan.launches.size(); ++li) {
+      const Launch& l = e.plan.launches[li];
       std::vector<uint64_t> values(l.args.size());
-      std::vector<std::unique_ptr<TensorMap>> maps;
       std::vector<void*> ptrs(l.args.size());
       for (size_t a = 0; a < l.args.size(); ++a) {
         const KernelArg& arg = l.args[a];
         if (arg.tensor_map) {
-          auto map = std::make_unique<TensorMap>();
           const KernelArg::Tma& t = arg.tma;
-          const uint32_t elem_strides[5] = {1, 1, 1, 1, 1};
-          const int dtype = t.elem_bytes == 2 ? 9 /* BFLOAT16 */ : (t.elem_bytes == 4 ? 7 /* FLOAT32 */ : 0);
-          CUresult_t r = d.cuTensorMapEncodeTiled(map.get(), dtype, static_cast<unsigned>(t.rank),
-                                                  reinterpret_cast<void*>(e.bound[t.slot]), t.dims, t.strides, t.box,
-                                                  elem_strides, 0, t.swizzle, 2 /* L2 128B promotion */, 0);
-          check(r, "cuTensorMapEncodeTiled");
-          ptrs[a] = map.get();
-          maps.push_back(std::move(map));
+          Entry::CachedMap& cached = e.map_cache[li][a];
+          if (!cached.valid || cached.base != e.bound[t.slot]) {
+            const uint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+            const int dtype = t.elem_bytes == 2 ? 9 /* BFLOAT16 */ : (t.elem_bytes == 4 ? 7 /* FLOAT32 */ : 0);
+            cached.valid = false;
+            CUresult_t r = d.cuTensorMapEncodeTiled(&cached.map, dtype, static_cast<unsigned>(t.rank),
+                                                    reinterpret_cast<void*>(e.bound[t.slot]), t.dims, t.strides, t.box,
+                                                    elem_strides, 0, t.swizzle, 2 /* L2 128B promotion */, 0);
+            check(r, "cuTensorMapEncodeTiled");
+            cached.base = e.bound[t.slot];
+            cached.valid = true;
+          }
+          ptrs[a] = &cached.map;
         } else if (arg.is_slot) {
           values[a] = arg.slot == -2 ? status_word : e.bound[arg.slot];
           ptrs[a] = &values[a];
@@ -674,6 +691,8 @@ uint32_t accy_b200_session_invoke_device(accy_b200_session* s, uint64_t handle, 
   return guarded(s, [&] {
     Entry& e = s->entryOf(handle);
     checkCounts(e, input_count, output_count);
+    if ((input_count && !input_ptrs) || (output_count && !output_ptrs))
+      throw StatusError{ACCY_B200_INVALID_BUFFER, "null pointer array"};
     s->ensureDevice();
     const DriverTable& d = driver();
     s->check(d.cuCtxSetCurrent(s->context), "cuCtxSetCurrent");
@@ -906,6 +925,11 @@ uint32_t accy_b200_builder_reduce(accy_b200_builder* b, uint32_t x, uint32_t red
   return built(b, value, [&] { return b->builder.reduceNamed(x, codeOf<Reducer>(reducer, 3), namesOf(axes, axis_count)); });
 }
 
+uint32_t accy_b200_builder_reduce_with(accy_b200_builder* b, uint32_t x, uint32_t init, uint32_t reducer,
+                                       const char* const* axes, uint32_t axis_count, uint32_t* value) {
+  return built(b, value, [&] { return b->builder.reduceWith(x, init, codeOf<Reducer>(reducer, 3), namesOf(axes, axis_count)); });
+}
+
 uint32_t accy_b200_builder_mean(accy_b200_builder* b, uint32_t x, const char* const* axes, uint32_t axis_count, uint32_t* value) {
   return built(b, value, [&] { return b->builder.meanNamed(x, namesOf(axes, axis_count)); });
 }
@@ -1094,6 +1118,7 @@ void accy_b200_test_use_fake_driver(int32_t enable) { useFakeDriver(enable != 0)
 void accy_b200_test_fake_fail(const char* driver_function, int32_t after_calls) {
   fakeFailAfter(driver_function ? driver_function : "", after_calls);
 }
+void accy_b200_test_fake_device_status(int32_t value) { fakeDeviceStatus(value); }
 uint32_t accy_b200_test_fake_call_count(const char* driver_function) {
   // "nvrtcCompileProgram" counts real NVRTC runs of this process (cache hits, in memory or on disk, do not)
   if (driver_function && std::strcmp(driver_function, "nvrtcCompileProgram") == 0) return nvrtcCompileCount();

@@ -73,6 +73,18 @@ ShardInfo analyseShardAxis(const Program& p, const std::string& axis) {
             // allowed only as the program's final fold: the pieces' results combine with the
             // same reducer (sum: one all-reduce that adds; max / min: one that takes the extreme)
             const uint32_t fold = 1u + static_cast<uint32_t>(op.sub);
+            if (static_cast<Reducer>(op.sub) == Reducer::sum) {
+              // every piece folds the recorded initial value again and the all-reduce adds the
+              // pieces, so a sum may be cut only when it starts from zero (a max or min may start
+              // anywhere: taking the same value in twice changes nothing)
+              const Operation& init = p.ops[op.operands[1]];
+              bool zero = init.kind == Kind::constant;
+              for (uint8_t byte : init.payload) zero = zero && byte == 0;
+              if (!zero) {
+                info.reason = "the axis is summed from a non-zero initial value, which every piece would add again";
+                return info;
+              }
+            }
             if (is_output[op.id] && (info.partial_fold == 0 || info.partial_fold == fold)) {
               info.partial_fold = fold;
               info.partial_outputs.push_back(op.id);

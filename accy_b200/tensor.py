@@ -210,6 +210,12 @@ class Value:
         names, count = _axes(axes)
         return self.builder._emit(lib.accy_b200_builder_reduce, self.id, REDUCER.index(reducer), names, count)
 
+    def reduce(self, init, reducer, axes):
+        """Value.reduce (value.zig:60-61): fold over `axes` with `reducer`, starting from the rank-0 value `init`."""
+        names, count = _axes(axes)
+        b = self.builder
+        return b._emit(lib.accy_b200_builder_reduce_with, self.id, b._check(init), REDUCER.index(reducer), names, count)
+
     def max(self, other):
         return self._bin("max", other) if isinstance(other, Value) else self._reduce("max", other)
 

@@ -63,9 +63,6 @@ typedef struct accy_b200_options {
   int32_t force_simt_gemm;    /* 1 = never use the tcgen05 kernels (exact k-serial order) */
   int32_t row_min_blocks;     /* schedule override: resident CTAs per SM requested of row kernels, 0 = automatic */
   int32_t single_shot_invoke; /* 1 = host-buffer invoke never streams the program through the GPU in chunks */
-  int32_t attention_poly;     /* attention schedule (experiments): low three bits = share of exponentials computed by
-                                 polynomial on the FMA pipe instead of the special-function unit (0 = automatic, 1 = none,
-                                 2 = 1/8, 3 = 1/4, 4 = 1/2); +8 = hand P to the MMA issuer in one piece, not two halves */
 } accy_b200_options;
 
 /* One input or output slot: session.zig:66-74 (Descriptor). */
@@ -166,6 +163,10 @@ uint32_t accy_b200_builder_compare(accy_b200_builder* b, uint32_t direction, uin
 uint32_t accy_b200_builder_select(accy_b200_builder* b, uint32_t pred, uint32_t on_true, uint32_t on_false, uint32_t* value);
 uint32_t accy_b200_builder_reduce(accy_b200_builder* b, uint32_t x, uint32_t reducer, const char* const* axes,
                                   uint32_t axis_count, uint32_t* value);
+/* Builder.reduceWith (src/tensor/trace/builder.zig:589-603; Value.reduce, value.zig:60-61): a fold over
+ * the named axes that starts from the rank-0 value `init` instead of the reducer's own start value. */
+uint32_t accy_b200_builder_reduce_with(accy_b200_builder* b, uint32_t x, uint32_t init, uint32_t reducer,
+                                       const char* const* axes, uint32_t axis_count, uint32_t* value);
 uint32_t accy_b200_builder_mean(accy_b200_builder* b, uint32_t x, const char* const* axes, uint32_t axis_count,
                                 uint32_t* value);
 uint32_t accy_b200_builder_contract(accy_b200_builder* b, uint32_t lhs, uint32_t rhs, const char* const* axes,
@@ -242,9 +243,20 @@ uint32_t accy_b200_wire_describe(const uint8_t* actp, size_t length, char* out, 
  * guesses * splits <= 262144, otherwise ACCY_B200_INVALID_BUFFER with a message in `error`.
  * The call is asynchronous on `stream`.  Calls on one device share the array: issue them one
  * after another, never overlapping.  The first call on a device looks up the array's device
- * address; make it outside stream capture. */
+ * address; make it outside stream capture.  A CUDA runtime error that the caller's own earlier calls
+ * left pending on the calling thread is returned (and cleared) as ACCY_B200_LAUNCH_FAILED with a
+ * message that says so, and nothing is launched; each of the two launches is checked by itself. */
 uint32_t accy_b200_mismatch_noalloc(const float* frequency, const float* time, const float* sample, float* out,
                                     uint64_t guesses, uint64_t points, uint32_t splits, void* stream,
+                                    char* error, size_t error_capacity);
+
+/* ---- measurement support ----
+ * No counterpart in the reference (which ships no benchmarks, src/root.zig:76-78).  Runs two
+ * register-only micro-kernels on the current CUDA device and `stream` and returns the ceilings the
+ * FP32-bound row kernels are reported against: (guess, point) pairs per second of a loop that does
+ * nothing but `sinf(f * t) - s`, square and add with CUDA's own sinf ("sinf + 4 flop"), and the
+ * flop/s of independent packed fma.rn.f32x2 chains.  Allocates nothing; synchronises `stream`. */
+uint32_t accy_b200_probe_fp32_rates(void* stream, double* sinf_pairs_per_second, double* packed_fma_flops,
                                     char* error, size_t error_capacity);
 
 /* ---- test support: a recording fake of the CUDA driver (the reference tests its CUDA backend
@@ -252,6 +264,9 @@ uint32_t accy_b200_mismatch_noalloc(const float* frequency, const float* time, c
 void accy_b200_test_use_fake_driver(int32_t enable);
 void accy_b200_test_fake_fail(const char* driver_function, int32_t after_calls);
 uint32_t accy_b200_test_fake_call_count(const char* driver_function);
+/* The fake's device status word reads as `value` from now on (0 = as stored): stands for a kernel
+ * whose bounded wait ran out (runtime.zig:279-314 is the reference's poisoning after a failed call). */
+void accy_b200_test_fake_device_status(int32_t value);
 
 const char* accy_b200_version(void);
 

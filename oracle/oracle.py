@@ -435,3 +435,52 @@ def describe(wire):
         lines.append("%d %s %s[%s]%s" % (op.id, op.kind, op.dtype, dims, operands))
     lines.append("outputs" + "".join(" %%%d" % o for o in outputs))
     return "\n".join(lines) + "\n"
+
+
+# ---------------------------------------------------------------------------------------------
+# sampled rows of the bf16 benchmark programs (full benchmark sizes in seconds of CPU time)
+# ---------------------------------------------------------------------------------------------
+def _index_array(values):
+    return np.ascontiguousarray(np.asarray(values, dtype=np.uint64))
+
+
+def matmul_rows(a_bits, b_bits, rows):
+    """Rows `rows` of A.B for bf16 bit patterns a [m, k], b [k, n]: f32 [len(rows), n], every element
+    folded k-serially in f32 (dot.zig:2049-2115), not narrowed."""
+    a_bits, b_bits = np.ascontiguousarray(a_bits), np.ascontiguousarray(b_bits)
+    k, n = b_bits.shape
+    idx = _index_array(rows)
+    out = np.zeros((len(idx), n), np.float32)
+    lib().oracle_matmul_bf16_rows(_ptr(a_bits), _ptr(b_bits), _ptr(out), ctypes.c_size_t(k), ctypes.c_size_t(n),
+                                  _ptr(idx), ctypes.c_size_t(len(idx)))
+    return out
+
+
+def attention_rows(q_bits, k_bits, v_bits, heads, queries, scale, causal):
+    """Output rows (head index over the merged leading axes, query index) of softmax(scale q.k^T [masked]).v
+    for bf16 bit patterns [..., seq, dim]: f32 [len(heads), dim] (attention.zig:473-509)."""
+    q_bits, k_bits, v_bits = (np.ascontiguousarray(x) for x in (q_bits, k_bits, v_bits))
+    q_len, dim = q_bits.shape[-2:]
+    k_len = k_bits.shape[-2]
+    h, r = _index_array(heads), _index_array(queries)
+    out = np.zeros((len(h), dim), np.float32)
+    threads = max(1, lib().oracle_max_threads())
+    scratch = np.zeros(threads * k_len, np.float32)
+    lib().oracle_attention_bf16_rows(_ptr(q_bits), _ptr(k_bits), _ptr(v_bits), _ptr(out), ctypes.c_size_t(q_len),
+                                     ctypes.c_size_t(k_len), ctypes.c_size_t(dim), ctypes.c_float(float(scale)),
+                                     ctypes.c_int(1 if causal else 0), _ptr(h), _ptr(r), ctypes.c_size_t(len(h)),
+                                     _ptr(scratch))
+    return out
+
+
+def mlp_rows(x, w1, b1, w2, b2, g, rows, eps=1e-6):
+    """Tokens `rows` of the two-layer MLP + RMSNorm program on bf16 bit patterns: f32 [len(rows), d]."""
+    x, w1, b1, w2, b2, g = (np.ascontiguousarray(a) for a in (x, w1, b1, w2, b2, g))
+    d, h = w1.shape
+    idx = _index_array(rows)
+    out = np.zeros((len(idx), d), np.float32)
+    hidden = np.zeros((len(idx), h), np.float32)
+    lib().oracle_mlp_bf16_rows(_ptr(x), _ptr(w1), _ptr(b1), _ptr(w2), _ptr(b2), _ptr(g), _ptr(out), _ptr(hidden),
+                               ctypes.c_size_t(d), ctypes.c_size_t(h), ctypes.c_float(eps), _ptr(idx),
+                               ctypes.c_size_t(len(idx)))
+    return out

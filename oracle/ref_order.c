@@ -27,7 +27,10 @@
  * Build: gcc -O2 -fno-fast-math -ffp-contract=off -shared -fPIC (see oracle/build.py).
  *
  * Pinning: the reference's shipped known answers for this path (the 16-sample mismatch values
- * 8.656 / 0 and the f32 [2,3]x[3,2] dot {58,64,139,154}) are checked in tests/test_oracle.py.
+ * 8.656 / 0 and the f32 [2,3]x[3,2] dot {58,64,139,154}) are checked in tests/test_cpu_suite.py
+ * (test_oracle_mismatch_known_answers, test_oracle_dot_known_answer), and a second, independently
+ * written restatement of the attention, normalisation and GELU formulas (tests/second_opinion.py)
+ * is compared with this file there.
  * Everything else is "parity unpinned": no other golden vector ships with the reference.
  */
 #include <math.h>
@@ -244,26 +247,64 @@ void oracle_softmax_layernorm_f32(const float* x, float* out, size_t rows, size_
   }
 }
 
-/* bf16 matmul oracle: f32 k-serial dot of the widened bf16 inputs, output left in f32 */
+/* bf16 matmul oracle: f32 k-serial dot of the widened bf16 inputs, output left in f32.  Every
+ * output element folds k in increasing order as acc = acc + a*b (dot.zig:2049-2115); the loops
+ * run k outside and n inside only so that B is read along its rows, which changes no element's
+ * own order of operations. */
+static void matmul_row_bf16(const uint16_t* a_row, const uint16_t* b, float* c_row, size_t k, size_t n) {
+  for (size_t ni = 0; ni < n; ++ni) c_row[ni] = 0.0f;
+  for (size_t ki = 0; ki < k; ++ki) {
+    const float av = bf16_to_f32(a_row[ki]);
+    const uint16_t* b_row = b + ki * n;
+    for (size_t ni = 0; ni < n; ++ni) {
+      float prod = av * bf16_to_f32(b_row[ni]);
+      c_row[ni] = c_row[ni] + prod;
+    }
+  }
+}
+
 void oracle_matmul_bf16(const uint16_t* a, const uint16_t* b, float* c, size_t m, size_t k, size_t n,
                         size_t row_begin, size_t row_end) {
   if (row_end > m) row_end = m;
 #pragma omp parallel for schedule(static)
-  for (size_t mi = row_begin; mi < row_end; ++mi) {
-    for (size_t ni = 0; ni < n; ++ni) {
-      float acc = 0.0f;
-      for (size_t ki = 0; ki < k; ++ki) {
-        float prod = bf16_to_f32(a[mi * k + ki]) * bf16_to_f32(b[ki * n + ni]);
-        acc = acc + prod;
-      }
-      c[mi * n + ni] = acc;
-    }
-  }
+  for (size_t mi = row_begin; mi < row_end; ++mi) matmul_row_bf16(a + mi * k, b, c + mi * n, k, n);
+}
+
+/* the same for a list of rows of A: c is [n_rows][n], row i of it is row rows[i] of the product */
+void oracle_matmul_bf16_rows(const uint16_t* a, const uint16_t* b, float* c, size_t k, size_t n,
+                             const size_t* rows, size_t n_rows) {
+#pragma omp parallel for schedule(dynamic)
+  for (size_t i = 0; i < n_rows; ++i) matmul_row_bf16(a + rows[i] * k, b, c + i * n, k, n);
 }
 
 /* scaled-dot-product attention in f32 on widened bf16 inputs, [batch][seq][dim] layouts,
  * following attention.zig:473-509 (scores, running max, exp sum, weighted sum), with the
  * optional causal mask (key <= query) applied as -inf before the max */
+static void attention_row_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, float* out_row, size_t b,
+                               size_t qi, size_t q_len, size_t k_len, size_t dim, float scale, int causal,
+                               float* scores) {
+  float max_score = -INFINITY;
+  for (size_t ki = 0; ki < k_len; ++ki) {
+    float dot = 0.0f;
+    for (size_t d = 0; d < dim; ++d)
+      dot += bf16_to_f32(q[(b * q_len + qi) * dim + d]) * bf16_to_f32(k[(b * k_len + ki) * dim + d]);
+    float score = dot * scale;
+    if (causal && ki > qi) score = -INFINITY;
+    scores[ki] = score;
+    if (score > max_score) max_score = score;
+  }
+  float denominator = 0.0f;
+  for (size_t ki = 0; ki < k_len; ++ki) denominator += expf(scores[ki] - max_score);
+  for (size_t d = 0; d < dim; ++d) {
+    float sum = 0.0f;
+    for (size_t ki = 0; ki < k_len; ++ki) {
+      float weight = expf(scores[ki] - max_score) / denominator;
+      sum += weight * bf16_to_f32(v[(b * k_len + ki) * dim + d]);
+    }
+    out_row[d] = sum;
+  }
+}
+
 void oracle_attention_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, float* out, size_t batch,
                            size_t q_len, size_t k_len, size_t dim, float scale, int causal,
                            size_t batch_begin, size_t batch_end, float* scratch /* threads*k_len */) {
@@ -276,27 +317,23 @@ void oracle_attention_bf16(const uint16_t* q, const uint16_t* k, const uint16_t*
 #else
       float* scores = scratch;
 #endif
-      float max_score = -INFINITY;
-      for (size_t ki = 0; ki < k_len; ++ki) {
-        float dot = 0.0f;
-        for (size_t d = 0; d < dim; ++d)
-          dot += bf16_to_f32(q[(b * q_len + qi) * dim + d]) * bf16_to_f32(k[(b * k_len + ki) * dim + d]);
-        float score = dot * scale;
-        if (causal && ki > qi) score = -INFINITY;
-        scores[ki] = score;
-        if (score > max_score) max_score = score;
-      }
-      float denominator = 0.0f;
-      for (size_t ki = 0; ki < k_len; ++ki) denominator += expf(scores[ki] - max_score);
-      for (size_t d = 0; d < dim; ++d) {
-        float sum = 0.0f;
-        for (size_t ki = 0; ki < k_len; ++ki) {
-          float weight = expf(scores[ki] - max_score) / denominator;
-          sum += weight * bf16_to_f32(v[(b * k_len + ki) * dim + d]);
-        }
-        out[(b * q_len + qi) * dim + d] = sum;
-      }
+      attention_row_bf16(q, k, v, out + (b * q_len + qi) * dim, b, qi, q_len, k_len, dim, scale, causal, scores);
     }
+  }
+}
+
+/* the same for a list of (batch-and-head index, query index) pairs: out is [n_rows][dim] */
+void oracle_attention_bf16_rows(const uint16_t* q, const uint16_t* k, const uint16_t* v, float* out, size_t q_len,
+                                size_t k_len, size_t dim, float scale, int causal, const size_t* heads,
+                                const size_t* queries, size_t n_rows, float* scratch /* threads*k_len */) {
+#pragma omp parallel for schedule(dynamic)
+  for (size_t i = 0; i < n_rows; ++i) {
+#ifdef _OPENMP
+    float* scores = scratch + (size_t)omp_get_thread_num() * k_len;
+#else
+    float* scores = scratch;
+#endif
+    attention_row_bf16(q, k, v, out + i * dim, heads[i], queries[i], q_len, k_len, dim, scale, causal, scores);
   }
 }
 
@@ -314,31 +351,50 @@ static inline float gelu_tanh(float x) {
 }
 
 /* two-layer MLP in f32 on widened bf16 inputs: (x.W1 + b1) -> GELU-tanh -> .W2 + b2 -> RMSNorm*g
- * (normalization.zig:372-398: mean square + eps, sqrt, divide, then weight).  `hidden` is a
- * caller-provided [tokens_in_range][h] f32 buffer. */
+ * (normalization.zig:372-398: mean square + eps, sqrt, divide, then weight).  Both products fold
+ * their contracted axis serially per output element (dot.zig:2049-2115); the contracted index runs
+ * in the outer loop only so that the weights are read along their rows.  `hid` is [h] scratch. */
+static void mlp_token_bf16(const uint16_t* x_row, const uint16_t* w1, const uint16_t* b1, const uint16_t* w2,
+                           const uint16_t* b2, const uint16_t* g, float* y, float* hid, size_t d, size_t h, float eps) {
+  for (size_t j = 0; j < h; ++j) hid[j] = 0.0f;
+  for (size_t i = 0; i < d; ++i) {
+    const float xv = bf16_to_f32(x_row[i]);
+    const uint16_t* w_row = w1 + i * h;
+    for (size_t j = 0; j < h; ++j) hid[j] = hid[j] + xv * bf16_to_f32(w_row[j]);
+  }
+  for (size_t j = 0; j < h; ++j) hid[j] = gelu_tanh(hid[j] + bf16_to_f32(b1[j]));
+  for (size_t i = 0; i < d; ++i) y[i] = 0.0f;
+  for (size_t j = 0; j < h; ++j) {
+    const float hv = hid[j];
+    const uint16_t* w_row = w2 + j * d;
+    for (size_t i = 0; i < d; ++i) y[i] = y[i] + hv * bf16_to_f32(w_row[i]);
+  }
+  float sum_squares = 0.0f;
+  for (size_t i = 0; i < d; ++i) {
+    y[i] = y[i] + bf16_to_f32(b2[i]);
+    sum_squares = sum_squares + y[i] * y[i];
+  }
+  float root = sqrtf(sum_squares / (float)d + eps);
+  for (size_t i = 0; i < d; ++i) y[i] = y[i] / root * bf16_to_f32(g[i]);
+}
+
+/* `hidden` is a caller-provided [tokens_in_range][h] f32 buffer. */
 void oracle_mlp_bf16(const uint16_t* x, const uint16_t* w1, const uint16_t* b1, const uint16_t* w2,
                      const uint16_t* b2, const uint16_t* g, float* out, float* hidden, size_t tokens, size_t d,
                      size_t h, float eps, size_t token_begin, size_t token_end) {
   (void)tokens;
 #pragma omp parallel for schedule(static)
-  for (size_t t = token_begin; t < token_end; ++t) {
-    float* hid = hidden + (t - token_begin) * h;
-    for (size_t j = 0; j < h; ++j) {
-      float acc = 0.0f;
-      for (size_t i = 0; i < d; ++i) acc = acc + bf16_to_f32(x[t * d + i]) * bf16_to_f32(w1[i * h + j]);
-      hid[j] = gelu_tanh(acc + bf16_to_f32(b1[j]));
-    }
-    float* y = out + t * d;
-    float sum_squares = 0.0f;
-    for (size_t i = 0; i < d; ++i) {
-      float acc = 0.0f;
-      for (size_t j = 0; j < h; ++j) acc = acc + hid[j] * bf16_to_f32(w2[j * d + i]);
-      y[i] = acc + bf16_to_f32(b2[i]);
-      sum_squares = sum_squares + y[i] * y[i];
-    }
-    float root = sqrtf(sum_squares / (float)d + eps);
-    for (size_t i = 0; i < d; ++i) y[i] = y[i] / root * bf16_to_f32(g[i]);
-  }
+  for (size_t t = token_begin; t < token_end; ++t)
+    mlp_token_bf16(x + t * d, w1, b1, w2, b2, g, out + t * d, hidden + (t - token_begin) * h, d, h, eps);
+}
+
+/* the same for a list of tokens: out is [n_rows][d], hidden [n_rows][h] */
+void oracle_mlp_bf16_rows(const uint16_t* x, const uint16_t* w1, const uint16_t* b1, const uint16_t* w2,
+                          const uint16_t* b2, const uint16_t* g, float* out, float* hidden, size_t d, size_t h,
+                          float eps, const size_t* rows, size_t n_rows) {
+#pragma omp parallel for schedule(dynamic)
+  for (size_t i = 0; i < n_rows; ++i)
+    mlp_token_bf16(x + rows[i] * d, w1, b1, w2, b2, g, out + i * d, hidden + i * h, d, h, eps);
 }
 
 int oracle_max_threads(void) {

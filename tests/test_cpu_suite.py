@@ -216,6 +216,124 @@ def test_oracle_config_loops_agree_with_the_program_evaluator():
 
 
 # ---------------------------------------------------------------------------------------------
+# the oracle against a second restatement written separately from the reference's text
+# (tests/second_opinion.py): attention.zig:473-509, normalization.zig:372-398,560-590,
+# elementwise.zig:125-135, dot.zig:2049-2115.  Both use one float32 operation per recorded
+# operation; only the exp / tanh routines differ (numpy's against glibc's, an ulp apart at most),
+# so results agree to a few ulp, up to 1e-5 (the f32 tolerance) where a weighted sum cancels.
+# ---------------------------------------------------------------------------------------------
+def _close(a, b, rel=1e-5):
+    a, b = np.asarray(a, np.float64).reshape(-1), np.asarray(b, np.float64).reshape(-1)
+    return float(np.max(np.abs(a - b) / np.maximum(np.abs(b), 1e-3 * np.abs(b).max()))) < rel
+
+
+def test_oracle_attention_agrees_with_a_second_restatement_on_the_reference_spec():
+    """The reference's own SDPA spec (attention.zig:464-471: batch 2, queries 2, keys 3, qk 2, value 2)
+    and a larger causal case, f32, through the program evaluator and through the C loop."""
+    import second_opinion
+    for (batch, nq, nk, qk, nv, causal) in [(2, 2, 3, 2, 2, False), (3, 9, 9, 8, 5, True), (1, 6, 11, 4, 3, False)]:
+        rng = np.random.default_rng(nq * 10 + nk)
+        # eighths in [-2, 2]: exact in bf16 too, so the bf16 C loop sees the very same numbers
+        q = (rng.integers(-16, 17, (batch, nq, qk)) / 8.0).astype(np.float32)
+        k = (rng.integers(-16, 17, (batch, nk, qk)) / 8.0).astype(np.float32)
+        v = (rng.integers(-16, 17, (batch, nk, nv)) / 8.0).astype(np.float32)
+        want = second_opinion.sdpa(q, k, v, causal)
+        scale = float(np.float32(1.0 / np.sqrt(float(qk))))
+
+        def body(b, a, scale=scale, causal=causal):
+            scores = a[0].contract(a[1], "dim").mul(b.scalar("f32", scale))
+            if causal:
+                dims = [d for d in scores.ty.dims if d[0] in ("seq", "key")]
+                mask = b.iota("i32", dims, "seq").compare("ge", b.iota("i32", dims, "key"))
+                scores = mask.select(scores, b.scalar("f32", -np.inf))
+            e = scores.sub(scores.max("key")).exp()
+            return e.div(e.sum("key")).contract(a[2].rename("dim", "value"), "key")
+        program = tensor.define("sdpa_spec", [tensor.spec("f32", batch=batch, seq=nq, dim=qk),
+                                              tensor.spec("f32", batch=batch, key=nk, dim=qk),
+                                              tensor.spec("f32", batch=batch, key=nk, dim=nv)], body)
+        got = oracle.run(program.wire, [q, k, v], mode="ref")[0].reshape(batch, nq, nv)
+        assert _close(got, want)
+        if qk == nv:
+            continue   # the C loop takes one dim for keys and values: checked on the square cases below
+    # the C loop (bf16 bit patterns in, f32 out) on inputs that are exact in bf16
+    o = oracle.lib()
+    size = ctypes.c_size_t
+    for (batch, n, dim, causal) in [(2, 3, 2, False), (2, 12, 8, True)]:
+        rng = np.random.default_rng(n)
+        q, k, v = [(rng.integers(-16, 17, (batch, n, dim)) / 8.0).astype(np.float32) for _ in range(3)]
+        bits = [configs.f32_to_bf16_bits(a) for a in (q, k, v)]
+        assert all(np.array_equal(configs.bf16_bits_to_f32(b), a) for a, b in zip((q, k, v), bits))
+        out = np.zeros((batch, n, dim), np.float32)
+        scratch = np.zeros(n * o.oracle_max_threads(), np.float32)
+        o.oracle_attention_bf16(*[b.ctypes.data_as(ctypes.c_void_p) for b in bits], out.ctypes.data_as(ctypes.c_void_p),
+                                size(batch), size(n), size(n), size(dim), ctypes.c_float(float(np.float32(1.0 / np.sqrt(float(dim))))),
+                                ctypes.c_int(1 if causal else 0), size(0), size(batch), scratch.ctypes.data_as(ctypes.c_void_p))
+        assert _close(out, second_opinion.sdpa(q, k, v, causal))
+        rows = oracle.attention_rows(bits[0], bits[1], bits[2], [0, batch - 1], [n - 1, 1],
+                                     float(np.float32(1.0 / np.sqrt(float(dim)))), causal)
+        assert np.array_equal(rows, np.stack([out[0, n - 1], out[batch - 1, 1]]))
+
+
+def test_oracle_row_formulas_agree_with_a_second_restatement():
+    import second_opinion
+    rng = np.random.default_rng(77)
+    x = (rng.standard_normal((5, 48)) * 3.0).astype(np.float32)
+    want = np.stack([second_opinion.row_layer_norm(second_opinion.row_softmax(row), 1e-5) for row in x])
+    cfg = configs.softmax_layernorm(5, 48)
+    got = oracle.run(cfg.program().wire, [x], mode="ref")[0]
+    # softmax values are ~1/48 and their centred form cancels two digits: 1e-4 of the output's scale
+    assert float(np.max(np.abs(got - want))) < 1e-4 * float(np.abs(want).max())
+    o = oracle.lib()
+    out = np.zeros_like(x)
+    o.oracle_softmax_layernorm_f32(x.ctypes.data_as(ctypes.c_void_p), out.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(5),
+                                   ctypes.c_size_t(48), ctypes.c_float(1e-5), ctypes.c_size_t(0), ctypes.c_size_t(5))
+    assert float(np.max(np.abs(out - want))) < 1e-4 * float(np.abs(want).max())
+    # softmax alone, where nothing cancels
+    soft = tensor.define("softmax", [tensor.spec("f32", row=5, col=48)],
+                         lambda b, a: a[0].sub(a[0].max("col")).exp().div(a[0].sub(a[0].max("col")).exp().sum("col")))
+    assert _close(oracle.run(soft.wire, [x], mode="ref")[0], np.stack([second_opinion.row_softmax(r) for r in x]))
+
+
+def test_oracle_mlp_and_gelu_agree_with_a_second_restatement():
+    import second_opinion
+    rng = np.random.default_rng(78)
+    tokens, d, h = 3, 8, 16
+    # sixteenths: exact in bf16
+    x = (rng.integers(-32, 33, (tokens, d)) / 16.0).astype(np.float32)
+    w1 = (rng.integers(-16, 17, (d, h)) / 16.0).astype(np.float32)
+    w2 = (rng.integers(-16, 17, (h, d)) / 16.0).astype(np.float32)
+    b1 = (rng.integers(-8, 9, h) / 16.0).astype(np.float32)
+    b2 = (rng.integers(-8, 9, d) / 16.0).astype(np.float32)
+    g = (rng.integers(8, 25, d) / 16.0).astype(np.float32)
+    want = second_opinion.mlp_rms(x, w1, b1, w2, b2, g, 1e-6)
+    bits = [configs.f32_to_bf16_bits(a) for a in (x, w1, b1, w2, b2, g)]
+    got = oracle.mlp_rows(*bits, rows=[0, 1, 2])
+    assert _close(got, want)
+    # the same program in f32 through the generic evaluator (every op rounded on its own)
+    program = tensor.define("mlp_f32", [tensor.spec("f32", token=tokens, d=d), tensor.spec("f32", d=d, h=h), tensor.spec("f32", h=h),
+                                        tensor.spec("f32", h=h, d=d), tensor.spec("f32", d=d), tensor.spec("f32", d=d)],
+                            configs.mlp_body)
+    ref = oracle.run(program.wire, [x, w1, b1, w2, b2, g], mode="ref")[0]
+    assert _close(ref, want)
+    # tanh-GELU alone over a range of arguments
+    values = np.linspace(-6.0, 6.0, 97).astype(np.float32)
+    gelu = tensor.define("gelu", [tensor.spec("f32", n=97)],
+                         lambda b, a: a[0].mul(b.scalar("f32", 0.5)).mul(
+                             a[0].add(a[0].mul(a[0]).mul(a[0]).mul(b.scalar("f32", 0.044715))).mul(b.scalar("f32", 0.7978845608028654)).tanh()
+                             .add(b.scalar("f32", 1.0))))
+    got = np.asarray(oracle.run(gelu.wire, [values], mode="ref")[0], np.float64)
+    want = np.array([second_opinion.gelu_tanh(v) for v in values], np.float64)
+    # gate = tanh + 1 cancels for negative arguments, so an ulp of tanh (the two libraries' tanh
+    # differ by that much) is an absolute 2^-24 * |x|: allow two of them
+    assert np.all(np.abs(got - want) <= 2.0 ** -23 * np.maximum(np.abs(values.astype(np.float64)), 1.0))
+    # the k-serial dot, bit for bit
+    a = rng.standard_normal((4, 37)).astype(np.float32)
+    b = rng.standard_normal((37, 5)).astype(np.float32)
+    dot = tensor.define("dot", [tensor.spec("f32", m=4, k=37), tensor.spec("f32", k=37, n=5)], configs.matmul_body)
+    assert np.array_equal(oracle.run(dot.wire, [a, b], mode="ref")[0], second_opinion.dot_serial(a, b))
+
+
+# ---------------------------------------------------------------------------------------------
 # fusion plans and sm_100a compilation (NVRTC, compile-only session)
 # ---------------------------------------------------------------------------------------------
 def plan_of(session, cfg, **kw):
@@ -454,6 +572,38 @@ def test_failed_launch_poisons_the_session(fake_driver):
         session.invoke(compiled, cfg.make_inputs(), [out])
     assert "poisoned" in e.value.message
     session.deinit()
+
+
+def test_a_kernel_that_gives_up_on_a_wait_poisons_the_session(fake_driver):
+    """The tcgen05 kernels bound every wait; when one runs out the kernel writes a code into the
+    session's device status word and returns.  The host reads the word after synchronising: a
+    non-zero code is `launch_failed`, the results are not handed out as valid, and the session
+    refuses further launches (stream poisoning, runtime.zig:279-314)."""
+    session = tensor.Session(device=0)
+    cfg = configs.matmul(256, 256, 256)
+    compiled = session.compile(cfg.program())
+    out = np.zeros(256 * 256, np.uint16)
+    session.invoke(compiled, cfg.make_inputs(), [out])          # a clean run first
+    launches = lib.accy_b200_test_fake_call_count(b"cuLaunchKernel")
+    lib.accy_b200_test_fake_device_status(1)
+    with pytest.raises(tensor.SessionError) as e:
+        session.invoke(compiled, cfg.make_inputs(), [out])
+    assert e.value.name == "launch_failed" and "bounded wait" in e.value.message and "status 1" in e.value.message
+    lib.accy_b200_test_fake_device_status(0)
+    after = lib.accy_b200_test_fake_call_count(b"cuLaunchKernel")
+    assert after == launches + 1
+    for call in (lambda: session.invoke(compiled, cfg.make_inputs(), [out]),
+                 lambda: session.invoke_device(compiled, [256, 512], [768])):
+        with pytest.raises(tensor.SessionError) as e:
+            call()
+        assert e.value.name == "launch_failed" and "poisoned" in e.value.message
+    assert lib.accy_b200_test_fake_call_count(b"cuLaunchKernel") == after   # nothing reached the device
+    session.deinit()
+    # a new session on the same device starts clean
+    fresh = tensor.Session(device=0)
+    again = fresh.compile(cfg.program())
+    fresh.invoke(again, cfg.make_inputs(), [out])
+    fresh.deinit()
 
 
 def test_at_most_64_programs_per_session(cpu_session):

@@ -7,6 +7,7 @@ import pytest
 
 from accy_b200 import tensor
 from oracle import oracle
+from parity_checks import check_three_distances
 
 T = tensor
 
@@ -56,6 +57,18 @@ CASES = {
     # a sine and a cosine of the same value: the joint routine, both results stored
     "sine_and_cosine": ([T.spec("f32", n=4096)], lambda b, a: sine_and_cosine(a[0].mul(b.scalar("f32", 40.0)))),
     "two_stage_reduce": ([T.spec("f32", a=50, b=70)], lambda b, a: a[0].sum("b").max("a")),
+    # Value.reduce with a recorded start value that is not the reducer's own (Builder.reduceWith): the
+    # reference folds it in once per result (reduction.zig:839-863), whatever the thread count
+    "sum_from_five": ([T.spec("f32", r=64, c=1024)], lambda b, a: a[0].reduce(b.scalar("f32", 5.0), "sum", "c")),
+    "sum_from_five_in_column_splits": ([T.spec("f32", r=3, c=1 << 18)],
+                                       lambda b, a: a[0].reduce(b.scalar("f32", 5.0), "sum", "c")),
+    "max_from_one_and_min_from_zero": ([T.spec("f32", r=40, c=300)],
+                                       lambda b, a: [a[0].mul(b.scalar("f32", 0.25)).reduce(b.scalar("f32", 1.0), "max", "c"),
+                                                     a[0].reduce(b.scalar("f32", 0.0), "min", "c")]),
+    "int_sum_from_seven": ([T.spec("i32", r=9, c=1000)], lambda b, a: a[0].reduce(b.scalar("i32", 7), "sum", "c")),
+    "row_pipeline_with_start_values": ([T.spec("f32", r=32, c=512)],
+                                       lambda b, a: a[0].sub(a[0].reduce(b.scalar("f32", 0.5), "max", "c")).exp()
+                                       .div(a[0].exp().reduce(b.scalar("f32", 3.0), "sum", "c"))),
     "softmax_then_colsum": ([T.spec("f32", r=64, c=128)],
                             lambda b, a: a[0].sub(a[0].max("c")).exp().div(a[0].sub(a[0].max("c")).exp().sum("c")).sum("r")),
 }
@@ -88,6 +101,25 @@ def test_compiles_for_sm100a(cpu_session, name):
     cpu_session.release(compiled)
 
 
+def test_recorded_start_value_is_folded_once_per_row(cpu_session):
+    """Per-thread accumulators start from the reducer's identity; the recorded 5.0 (0x40a00000)
+    appears in one fold behind the tree, and with column splits only in the combine kernel."""
+    for name in ("sum_from_five", "sum_from_five_in_column_splits"):
+        specs, body = CASES[name]
+        compiled = cpu_session.compile(tensor.define(name, specs, body))
+        sources = {n: src for n, src, _ in compiled.kernels()}
+        cpu_session.release(compiled)
+        main = [src for n, src in sources.items() if not n.endswith("_combine")]
+        combine = [src for n, src in sources.items() if n.endswith("_combine")]
+        assert len(main) == 1
+        assert "acc_" in main[0] and " = __uint_as_float(0x0u);" in main[0]
+        assert "= __uint_as_float(0x40a00000u);" not in main[0]
+        holder = combine[0] if combine else main[0]
+        assert holder.count("0x40a00000u") == 1 and "fold<0, float>(__uint_as_float(0x40a00000u)," in holder
+        if combine:
+            assert "0x40a00000u" not in main[0]
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_matches_oracle(gpu_session, name):
@@ -115,11 +147,8 @@ def test_matches_oracle(gpu_session, name):
         got = got_raw.view(np.float64 if ty.dtype == "f64" else np.float32).astype(np.float64)
         want64 = want.reshape(-1).astype(np.float64)
         ex64 = np.asarray(ex, np.float64).reshape(-1)
-        floor = max(np.abs(ex64).max() * (1e-3 if name in ("value_and_slope", "softmax_then_colsum") else 1e-6), 1e-30)
-        err_gpu = np.max(np.abs(got - ex64) / np.maximum(np.abs(ex64), floor))
-        err_ref = np.max(np.abs(want64 - ex64) / np.maximum(np.abs(ex64), floor))
-        tol = 1e-12 if ty.dtype == "f64" else 1e-5
-        assert err_gpu < tol + err_ref, (name, err_gpu, err_ref)
+        floor_frac = 1e-3 if name in ("value_and_slope", "softmax_then_colsum", "row_pipeline_with_start_values") else 1e-6
+        check_three_distances(name, got, want64, ex64, floor_frac, tol=1e-12 if ty.dtype == "f64" else 1e-5)
 
 
 # Zero-extent axes: the reference's type rules allow them (only negative extents are refused);

@@ -48,17 +48,24 @@ def _case(name):
         return _ColumnExtreme("max"), "row"
     if name == "column_minima":
         return _ColumnExtreme("min"), "row"
+    if name == "column_maxima_from_start":
+        return _ColumnExtreme("max", start=0.25), "row"
     return configs.mismatch(6, 128), "point"
 
 
 class _ColumnExtreme:
     """max / min over the sharded axis: the ranks' partial extremes combine with the same operation"""
 
-    def __init__(self, which):
+    def __init__(self, which, start=None):
         self.which = which
+        self.start = start
 
     def program(self):
         from accy_b200 import tensor
+        if self.start is not None:
+            # a recorded start value: every rank takes it in again, which an extreme does not mind
+            return tensor.define("column_" + self.which, [tensor.spec("f32", row=8, col=16)],
+                                 lambda b, a: a[0].reduce(b.scalar("f32", self.start), self.which, "row"))
         return tensor.define("column_" + self.which, [tensor.spec("f32", row=8, col=16)],
                              lambda b, a: getattr(a[0], self.which)("row"))
 
@@ -66,7 +73,7 @@ class _ColumnExtreme:
         return [np.random.default_rng(3).standard_normal((8, 16)).astype(np.float32)]
 
 
-@pytest.mark.parametrize("case", ["rows", "guesses", "points", "column_maxima", "column_minima"])
+@pytest.mark.parametrize("case", ["rows", "guesses", "points", "column_maxima", "column_minima", "column_maxima_from_start"])
 def test_two_ranks_reproduce_the_single_device_result(case, tmp_path):
     import torch.multiprocessing as mp
     world = 2
@@ -99,3 +106,22 @@ def test_shard_plan_slices():
     assert plan.output_slices(1) == [(0, 32)]
     with pytest.raises(Exception):
         shard.ShardPlan(program, "guess", 3)
+
+
+def test_a_sum_from_a_non_zero_start_is_not_cut_along_its_axis():
+    """Every piece would add the recorded start value again and the all-reduce would add the pieces:
+    total + world * start.  The shard planner refuses the axis; the kept axis still shards."""
+    from accy_b200 import tensor
+    program = tensor.define("sum_from_five", [tensor.spec("f32", row=8, col=16)],
+                            lambda b, a: a[0].reduce(b.scalar("f32", 5.0), "sum", "row"))
+    with pytest.raises(tensor.SessionError) as e:
+        shard.ShardPlan(program, "row", 2)
+    assert "initial value" in str(e.value)
+    kept = tensor.define("row_sums_from_five", [tensor.spec("f32", row=8, col=16)],
+                         lambda b, a: a[0].reduce(b.scalar("f32", 5.0), "sum", "col"))
+    plan = shard.ShardPlan(kept, "row", 2)
+    assert not plan.partial_sum
+    x = np.random.default_rng(5).standard_normal((8, 16)).astype(np.float32)
+    full = oracle.run(kept.wire, [x])[0]
+    halves = [oracle.run(plan.piece.wire, [np.ascontiguousarray(x[r * 4:(r + 1) * 4])])[0] for r in range(2)]
+    assert np.array_equal(np.concatenate(halves), full)

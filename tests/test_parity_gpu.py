@@ -14,6 +14,7 @@ import pytest
 
 from accy_b200 import configs, tensor
 from oracle import oracle
+from parity_checks import check_three_distances
 
 pytestmark = pytest.mark.gpu
 
@@ -52,7 +53,7 @@ def test_mismatch_matches_oracle(gpu_session, guesses, points):
     # the serial f32 fold of the reference carries its own rounding error of about sqrt(n)*eps;
     # the GPU's tree-shaped fold must be at least as close to the exact sum as 1e-5 relative
     assert rel_err(got, exact, 1e-6) < 1e-5
-    assert rel_err(got, ref, 1e-6) < 1e-5 + rel_err(ref, exact, 1e-6)
+    check_three_distances("mismatch %dx%d" % (guesses, points), got, ref, exact, 1e-6)
 
 
 def test_mismatch_readme_constants(gpu_session):
@@ -73,7 +74,7 @@ def test_softmax_layernorm_matches_oracle(gpu_session, rows, cols):
     got = outs[0].view(np.float32).reshape(rows, cols)
     ref = oracle.run(program.wire, inputs)[0]
     exact = oracle.run(program.wire, inputs, mode="f64")[0]
-    assert rel_err(got, exact, 1e-3) < 1e-5 + rel_err(ref, exact, 1e-3)
+    check_three_distances("softmax_layernorm %dx%d" % (rows, cols), got, ref, exact, 1e-3)
 
 
 @pytest.mark.parametrize("m,n,k", [(2, 2, 3), (96, 80, 72), (256, 256, 256), (128, 384, 192)])
@@ -313,14 +314,20 @@ def test_softmax_layernorm_full_size_properties(gpu_session):
     got = outs[0].view(np.float32).reshape(32768, 4096)
     assert np.all(np.isfinite(got))
     assert np.abs(got.mean(axis=1, dtype=np.float64)).max() < 1e-4
-    rows = np.array([0, 1, 4097, 16384, 32767])
+    rows = np.concatenate([[0, 1, 4097, 16384, 32767], np.random.default_rng(19).integers(0, 32768, 251)])
     sub = np.ascontiguousarray(inputs[0][rows])
     ref = np.zeros_like(sub)
     lib = oracle.lib()
     lib.oracle_softmax_layernorm_f32(sub.ctypes.data_as(ctypes.c_void_p), ref.ctypes.data_as(ctypes.c_void_p),
                                      ctypes.c_size_t(len(rows)), ctypes.c_size_t(4096), ctypes.c_float(1e-5),
                                      ctypes.c_size_t(0), ctypes.c_size_t(len(rows)))
-    assert rel_err(got[rows], ref, 1e-3) < 2e-5
+    # the exact rows: softmax then layer-norm in f64
+    x = sub.astype(np.float64)
+    e = np.exp(x - x.max(axis=1, keepdims=True))
+    y = e / e.sum(axis=1, keepdims=True)
+    c = y - y.mean(axis=1, keepdims=True)
+    exact = c / np.sqrt((c * c).mean(axis=1, keepdims=True) + 1e-5)
+    check_three_distances("softmax_layernorm 32768x4096, 256 rows", got[rows], ref, exact, 1e-3)
 
 
 def test_mismatch_full_size_sample(gpu_session):
@@ -336,6 +343,17 @@ def test_mismatch_full_size_sample(gpu_session):
                                      inputs[2].ctypes.data_as(ctypes.c_void_p), exact.ctypes.data_as(ctypes.c_void_p),
                                      ctypes.c_size_t(16), ctypes.c_size_t(65536))
     assert rel_err(got[:16], exact, 1e-6) < 1e-5
+    # 64 guesses spread over the whole output against the reference-order f32 fold as well
+    picks = np.linspace(0, 8191, 64).astype(np.int64)
+    f = np.ascontiguousarray(inputs[0][picks])
+    ref = np.zeros(64, np.float32)
+    exact = np.zeros(64, np.float64)
+    args = (inputs[1].ctypes.data_as(ctypes.c_void_p), inputs[2].ctypes.data_as(ctypes.c_void_p))
+    oracle.lib().oracle_mismatch_f32(f.ctypes.data_as(ctypes.c_void_p), args[0], args[1], ref.ctypes.data_as(ctypes.c_void_p),
+                                     ctypes.c_size_t(64), ctypes.c_size_t(65536), ctypes.c_size_t(0), ctypes.c_size_t(64))
+    oracle.lib().oracle_mismatch_f64(f.ctypes.data_as(ctypes.c_void_p), args[0], args[1], exact.ctypes.data_as(ctypes.c_void_p),
+                                     ctypes.c_size_t(64), ctypes.c_size_t(65536))
+    check_three_distances("mismatch 8192x65536, 64 guesses", got[picks], ref, exact, 1e-6)
 
 
 @pytest.mark.parametrize("make,kept", [(lambda: configs.mlp(256, 256, 512), [1, 2, 3, 4, 5]),

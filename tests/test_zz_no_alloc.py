@@ -6,8 +6,9 @@ keeps the partial sums of the two-pass column-split reduction in an array built 
 instead of a buffer allocated at load time.  This test calls it through the C ABI on buffers the
 test owns, twice in a row (the array is shared between calls and keeps the previous call's
 contents, so the second call must not be disturbed by the first), and compares each result with
-what the session path computes for the same recorded program, to the f32 tolerance of the other
-parity tests (1e-5 relative).  The file sorts last so that a run that stops at the first failure
+what the session path computes for the same recorded program and with the CPU oracle (the
+reference-order f32 fold and the f64 evaluation: two GPU paths could share a mistake, the oracle
+shares none), to the f32 tolerance of the other parity tests (1e-5 relative).  The file sorts last so that a run that stops at the first failure
 has already run everything else.
 """
 import ctypes
@@ -17,6 +18,8 @@ import pytest
 
 from accy_b200 import configs, tensor
 from accy_b200._native import lib
+from oracle import oracle
+from parity_checks import check_three_distances
 
 pytestmark = pytest.mark.gpu
 
@@ -58,6 +61,9 @@ def test_no_alloc_entry_point_matches_session_path_twice():
         torch.cuda.synchronize()
         got = out.cpu().numpy()
         assert rel_err(got, expected) < 1e-5
+        wire = cfg.program().wire
+        check_three_distances("no-alloc mismatch %dx%d" % (guesses, points), got, oracle.run(wire, inputs)[0],
+                              oracle.run(wire, inputs, mode="f64")[0], 1e-6)
 
 
 def test_no_alloc_entry_point_refuses_oversized_calls():

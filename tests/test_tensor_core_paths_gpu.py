@@ -1,6 +1,7 @@
-"""GPU parity of the tcgen05 kernels on the paths the benchmark runs: CTAs that take several
-output tiles (both accumulator buffers, accumulator phases 0 and 1), k extents that wrap the
-shared-memory stage ring several times, and the five BASELINE sizes themselves by sampled rows.
+"""GPU parity of the tcgen05 kernels on the paths the benchmark runs: CTAs (or CTA pairs, where two
+CTAs share a 256-row tile through cta_group::2) that take several output tiles (both accumulator
+buffers, accumulator phases 0 and 1), k extents that wrap the shared-memory stage ring several
+times, and the five BASELINE sizes themselves by sampled rows.
 
 The oracle side evaluates only the sampled rows (`oracle.matmul_rows`, `attention_rows`,
 `mlp_rows`: the same k-serial f32 folds of dot.zig:2049-2115 and the SDPA restatement of
@@ -73,6 +74,10 @@ MULTI_TILE_GEMMS = {
     "k_major_rhs": ((("m", 1536), ("k", 832)), (("n", 4096), ("k", 832))),
     # lhs stored [k, m] (M-major A tiles, what gradients of contractions read)
     "transposed_lhs": ((("k", 1024), ("m", 2048)), (("k", 1024), ("n", 4096))),
+    # one 128-row block: the one-CTA kernel (no CTA pair), 150 tiles of 128 x 256, 9 k-blocks
+    "single_row_block_many_columns": ((("m", 128), ("k", 576)), (("k", 576), ("n", 38400))),
+    # 257 rows: the second CTA pair's lower CTA has one row inside the matrix, the rest of its tile is outside
+    "one_row_past_a_pair": ((("m", 257), ("k", 640)), (("k", 640), ("n", 19456))),
 }
 
 

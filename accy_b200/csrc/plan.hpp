@@ -192,6 +192,7 @@ struct RowSchedule {
   int64_t chunks = 1;  // chunk iterations per row (1 = the whole row lives in registers)
   int splits = 1;      // CTAs sharing one row (deterministic two-pass combine when > 1)
   int min_blocks = 0;  // resident CTAs per SM asked of the compiler (caps registers), 0 = no request
+  int rpt = 1;         // rows per thread: neighbouring rows a thread folds together, sharing what does not vary along the rows
 };
 RowSchedule chooseRowSchedule(const Cluster& c, const ScheduleOverrides& o);
 void emitRowKernels(const Cluster& c, const RowSchedule& s, const std::string& name, Plan& plan,

@@ -632,6 +632,7 @@ class Planner {
     label << name << " rows=" << c.rows << " cols=" << c.cols << " reduces=" << countReduces(c)
           << " tpr=" << sched.tpr << " rpc=" << sched.rpc << " vec=" << sched.vec << " vpt=" << sched.vpt
           << " chunks=" << sched.chunks << " splits=" << sched.splits;
+    if (sched.rpt > 1) label << " rows_per_thread=" << sched.rpt;
     summary << "row kernel: " << label.str() << " outputs=" << out_values.size() << "\n";
     emitRowKernels(c, sched, name, plan, label.str());
     plan.work.pairs += static_cast<double>(c.rows) * static_cast<double>(c.cols);

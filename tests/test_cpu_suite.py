@@ -368,7 +368,15 @@ def test_matmul_uses_the_tcgen05_kernel(cpu_session):
     summary, work, kernels = plan_of(cpu_session, configs.matmul())
     assert "tcgen05" in summary and work["flops"] == 2.0 * 8192 ** 3
     src = kernels[0][1]
-    assert "tcgen05.mma.cta_group::1.kind::f16" in src and "cp.async.bulk.tensor.3d" in src
+    # a CTA pair per 256-row tile: paired MMAs, every TMA load without cluster multicast (each CTA
+    # loads its own operand halves; only the MMA-completion signal goes to both CTAs)
+    assert "tcgen05.mma.cta_group::2.kind::f16" in src and "__cluster_dims__(2, 1, 1)" in src
+    loads = [line for line in src.split("\n") if "cp.async.bulk.tensor" in line]
+    assert loads and not any("multicast" in line for line in loads)
+    # one 128-row block: the one-CTA kernel
+    summary, work, kernels = plan_of(cpu_session, configs.matmul(128, 512, 256))
+    src = kernels[0][1]
+    assert "tcgen05.mma.cta_group::1.kind::f16" in src and "cp.async.bulk.tensor.3d" in src and "__cluster_dims__" not in src
     assert "multicast" not in src
 
 

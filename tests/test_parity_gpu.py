@@ -431,3 +431,31 @@ def test_packed_sine_and_cosine_are_accurate_to_two_ulp(gpu_session):
                 want = fn(x64)
             assert np.all(np.isnan(got[~finite]))
             assert _ulps(got[finite], want[finite]).max() < 2.0, name
+
+
+def test_packed_exp_is_accurate_to_three_ulp(gpu_session):
+    """The row kernels' own exp (2^x of the special-function unit with the argument's rounding error
+    carried into the result): against f64 over the whole finite range, at the overflow and
+    underflow edges, and for infinities and NaN (where the thread falls back to expf).  Results
+    below 2^-126 may be flushed to zero (expf returns subnormal numbers there)."""
+    rng = np.random.default_rng(37)
+    n = 1 << 20
+    x = np.concatenate([rng.uniform(-104.0, 89.0, n // 2), rng.uniform(-30.0, 0.0, n // 4), rng.standard_normal(n // 4) * 3.0]).astype(np.float32)
+    x[:16] = [0.0, -0.0, np.inf, -np.inf, np.nan, 88.7, 88.73, 89.0, -87.0, -87.4, -90.0, -103.0, -110.0, 1e30, -1e30, 1.0]
+    program = tensor.define("packed_exp", [tensor.spec("f32", n=n)], lambda b, a: a[0].exp())
+    compiled = gpu_session.compile(program)
+    assert "ex2_ftz(-nh0)" in compiled.kernels()[0][1]
+    got = np.empty(n, np.float32)
+    gpu_session.invoke(compiled, [x], [got])
+    gpu_session.release(compiled)
+    with np.errstate(over="ignore", invalid="ignore"):
+        want = np.exp(x.astype(np.float64))
+    assert np.isnan(got[4]) and got[2] == np.inf and got[3] == 0.0 and got[13] == np.inf and got[14] == 0.0
+    assert got[0] == 1.0 and got[1] == 1.0
+    overflow = want > float(np.finfo(np.float32).max)
+    assert np.all(got[overflow & ~np.isnan(want)] == np.inf)
+    normal = np.isfinite(want) & (want >= 2.0 ** -126) & ~overflow
+    assert _ulps(got[normal], want[normal]).max() < 3.0
+    tiny = np.isfinite(want) & (want < 2.0 ** -126)
+    assert np.all(np.abs(got[tiny].astype(np.float64) - want[tiny]) <= 2.0 ** -126)
+    print("packed exp: max %.2f ulp, mean %.3f ulp" % (_ulps(got[normal], want[normal]).max(), _ulps(got[normal], want[normal]).mean()))

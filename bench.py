@@ -155,9 +155,12 @@ EXECUTED_FLOP_PER_PAIR = {"mismatch": 23.0, "refine": 33.0}
 RESIDENT_INPUTS = {"matmul": [1], "mlp": [1, 2, 3, 4, 5]}
 
 SMALL_SIZES = {
-    # profiling sizes: the same kernels, inputs still larger than L2 where the kernel is HBM-bound
-    "softmax_layernorm": (8192, 4096), "mismatch": (1024, 65536), "refine": (1024, 65536),
-    "matmul": (4096, 4096, 4096), "attention": (1, 16, 4096, 128), "mlp": (4096, 4096, 4096),
+    # profiling sizes: the same kernels and schedules as the full sizes, inputs still larger than L2
+    # where the kernel is HBM-bound, and whole rounds of work where a persistent kernel hands out
+    # tiles (matmul: 37 x 8 tiles of 256 x 256 = 4 per CTA pair; attention: 37 heads x 16 query
+    # pairs = 4 work items per CTA)
+    "softmax_layernorm": (8192, 4096), "mismatch": (4096, 65536), "refine": (4096, 65536),
+    "matmul": (9472, 2048, 4096), "attention": (1, 37, 4096, 128), "mlp": (4096, 4096, 4096),
 }
 SHARD_AXIS = {"mismatch": "guess", "refine": "guess", "softmax_layernorm": "row", "matmul": "m", "attention": "batch", "mlp": "token"}
 

@@ -83,6 +83,13 @@ PROTOTYPES = {
     "accy_b200_wire_vmap": (c_u32, [c_p, c_size, ctypes.c_int64, P(ctypes.c_int64), c_u32, c_u32, c_str, c_p, c_size,
                             P(c_size), c_p, c_size]),
     "accy_b200_wire_describe": (c_u32, [c_p, c_size, c_p, c_size, P(c_size)]),
+    "accy_b200_sharded_create": (c_u32, [P(ctypes.c_int32), c_u32, P(Options), P(c_p)]),
+    "accy_b200_sharded_destroy": (None, [c_p]),
+    "accy_b200_sharded_device_count": (c_u32, [c_p]),
+    "accy_b200_sharded_compile": (c_u32, [c_p, c_p, c_size, c_str, P(c_u64)]),
+    "accy_b200_sharded_invoke": (c_u32, [c_p, c_u64, P(c_p), P(c_size), c_u32, P(c_p), P(c_size), c_u32]),
+    "accy_b200_sharded_release": (c_u32, [c_p, c_u64]),
+    "accy_b200_sharded_last_error": (c_str, [c_p]),
     "accy_b200_mismatch_noalloc": (c_u32, [c_p, c_p, c_p, c_p, c_u64, c_u64, c_u32, c_p, c_p, c_size]),
     "accy_b200_probe_fp32_rates": (c_u32, [c_p, P(ctypes.c_double), P(ctypes.c_double), c_p, c_size]),
     "accy_b200_test_use_fake_driver": (None, [ctypes.c_int32]),

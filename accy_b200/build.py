@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libaccy_b200.so")
 SOURCES = ["program.cpp", "wire.cpp", "planner.cpp", "emit_row.cpp", "emit_gemm.cpp", "emit_tc.cpp", "emit_attn.cpp", "shard.cpp", "transform.cpp",
-           "driver.cpp", "session.cpp"]
+           "driver.cpp", "session.cpp", "sharded.cpp"]
 
 
 def needs_build():

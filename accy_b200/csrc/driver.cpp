@@ -74,7 +74,9 @@ void loadReal() {
 }
 
 // ---- fake driver: host memory stands for device memory, launches are only recorded ----
+std::mutex g_fake_mutex;   // sessions of several devices call the fake from their own host threads
 CUresult_t fakeResult(const char* fn) {
+  std::lock_guard<std::mutex> lock(g_fake_mutex);
   g_fake_calls[fn] += 1;
   auto it = g_fake_fail.find(fn);
   if (it != g_fake_fail.end()) {
@@ -221,6 +223,7 @@ const DriverTable& driver() {
 void useFakeDriver(bool enable) {
   std::lock_guard<std::mutex> lock(g_mutex);
   g_use_fake = enable;
+  std::lock_guard<std::mutex> fake_lock(g_fake_mutex);
   g_fake_calls.clear();
   g_fake_fail.clear();
   g_fake_device_status = 0;
@@ -232,13 +235,13 @@ void fakeDeviceStatus(int value) {
 }
 
 void fakeFailAfter(const std::string& function, int calls) {
-  std::lock_guard<std::mutex> lock(g_mutex);
+  std::lock_guard<std::mutex> lock(g_fake_mutex);
   if (calls < 0) g_fake_fail.erase(function);
   else g_fake_fail[function] = calls;
 }
 
 unsigned fakeCallCount(const std::string& function) {
-  std::lock_guard<std::mutex> lock(g_mutex);
+  std::lock_guard<std::mutex> lock(g_fake_mutex);
   auto it = g_fake_calls.find(function);
   return it == g_fake_calls.end() ? 0 : it->second;
 }

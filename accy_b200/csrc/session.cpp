@@ -538,7 +538,7 @@ uint32_t accy_b200_session_create(const accy_b200_options* options, accy_b200_se
 
 void accy_b200_session_destroy(accy_b200_session* s) {
   if (!s) return;
-  {
+  try {
     std::lock_guard<std::mutex> lock(s->mutex);
     for (Entry& e : s->entries)
       if (e.live) s->unload(e);
@@ -549,6 +549,8 @@ void accy_b200_session_destroy(accy_b200_session* s) {
       if (s->stream) d.cuStreamDestroy(s->stream);
       d.cuDevicePrimaryCtxRelease(s->device);
     }
+  } catch (const std::exception&) {
+    // the driver is gone (or was never there): nothing left to hand back
   }
   delete s;
 }

@@ -590,6 +590,63 @@ class Session:
         self._check(lib.accy_b200_session_release(self._h, compiled.handle))
 
 
+class MultiCuda:
+    """One recorded program over several GPUs of a box from one process (`accy_b200_sharded_*`):
+    the program is cut along `axis` into one piece per device, `launch` takes the buffers of the
+    WHOLE program (as `Cuda.launch` does) and drives all devices at once.  The reference runs on
+    one device only; this has no counterpart there."""
+
+    def __init__(self, program, axis, devices, **overrides):
+        opts = _native.Options()
+        for k, v in overrides.items():
+            setattr(opts, k, v)
+        ordinals = (ctypes.c_int32 * len(devices))(*devices)
+        self._h = ctypes.c_void_p()
+        status = lib.accy_b200_sharded_create(ordinals, len(devices), ctypes.byref(opts), ctypes.byref(self._h))
+        if status:
+            raise SessionError(status, "sharded_create")
+        wire_bytes = program.wire if isinstance(program, Program) else bytes(program)
+        handle = ctypes.c_uint64()
+        buf = ctypes.create_string_buffer(wire_bytes, len(wire_bytes))
+        try:
+            self._check(lib.accy_b200_sharded_compile(self._h, ctypes.cast(buf, ctypes.c_void_p), len(wire_bytes), axis.encode(),
+                                                      ctypes.byref(handle)))
+        except SessionError:
+            self.deinit()
+            raise
+        self.handle = handle.value
+
+    def _check(self, status):
+        if status:
+            raise SessionError(status, lib.accy_b200_sharded_last_error(self._h).decode(errors="replace"))
+
+    def launch(self, inputs, outputs):
+        keep = []
+        in_ptrs = (ctypes.c_void_p * max(1, len(inputs)))()
+        in_sizes = (ctypes.c_size_t * max(1, len(inputs)))()
+        for i, b in enumerate(inputs):
+            addr, size, k = _buffer_address(b, False)
+            in_ptrs[i], in_sizes[i] = addr, size
+            keep.append(k)
+        out_ptrs = (ctypes.c_void_p * max(1, len(outputs)))()
+        out_sizes = (ctypes.c_size_t * max(1, len(outputs)))()
+        for j, b in enumerate(outputs):
+            addr, size, k = _buffer_address(b, True)
+            out_ptrs[j], out_sizes[j] = addr, size
+            keep.append(k)
+        self._check(lib.accy_b200_sharded_invoke(self._h, self.handle, in_ptrs, in_sizes, len(inputs), out_ptrs, out_sizes,
+                                                 len(outputs)))
+
+    def deinit(self):
+        if self._h:
+            lib.accy_b200_sharded_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        if lib is not None:
+            self.deinit()
+
+
 class Cuda:
     """The B200 counterpart of the reference's `Cpu` executor (src/tensor/execute.zig:9-51):
     compile once in `__init__`, `launch` many times, `deinit` to free."""

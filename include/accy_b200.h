@@ -232,6 +232,29 @@ uint32_t accy_b200_wire_vmap(const uint8_t* actp, size_t length, int64_t axis_si
 uint32_t accy_b200_wire_describe(const uint8_t* actp, size_t length, char* out, size_t capacity,
                                  size_t* out_length);
 
+/* ---- one program over several GPUs, from one process ----
+ * No counterpart in the reference, which runs on one device and has no collective
+ * (deps/lib/compiler/gpu/src/runtime/cuda/runtime.zig:56-85 opens one ordinal).  The program is cut
+ * along the named axis into one piece per device (the analysis and the pieces of accy_b200_wire_shard);
+ * each device gets a session of its own and a host thread per invoke.  Buffers and sizes are those of
+ * the WHOLE program, as Session.invoke would take them (session.zig:163-226): buffers that carry the
+ * axis are used in place, block d by device d; the others are read by every device; when the axis is
+ * the one the outputs fold over, the devices' partial results are combined on the host in device
+ * order (sum, maximum or minimum, as recorded).  The axis extent must divide by the device count.
+ * `devices` may name one ordinal several times (pieces then share that GPU). */
+typedef struct accy_b200_sharded accy_b200_sharded;
+uint32_t accy_b200_sharded_create(const int32_t* devices, uint32_t device_count, const accy_b200_options* options,
+                                  accy_b200_sharded** sharded);
+void accy_b200_sharded_destroy(accy_b200_sharded* sharded);
+uint32_t accy_b200_sharded_device_count(accy_b200_sharded* sharded);
+uint32_t accy_b200_sharded_compile(accy_b200_sharded* sharded, const uint8_t* actp, size_t length, const char* axis,
+                                   uint64_t* handle);
+uint32_t accy_b200_sharded_invoke(accy_b200_sharded* sharded, uint64_t handle, const void* const* inputs,
+                                  const size_t* input_sizes, uint32_t input_count, void* const* outputs,
+                                  const size_t* output_sizes, uint32_t output_count);
+uint32_t accy_b200_sharded_release(accy_b200_sharded* sharded, uint64_t handle);
+const char* accy_b200_sharded_last_error(accy_b200_sharded* sharded);
+
 /* ---- allocation-free entry point ----
  * No counterpart in the reference.  For hosts that may not allocate device memory while running
  * (a service whose pool owns the whole device, a real-time loop, a fixed stream schedule): the

@@ -664,3 +664,34 @@ def test_shard_program_rules():
                       (configs.attention(4, 2, 8, 4), "batch"), (configs.mlp(8, 8, 16), "token")]:
         piece, partial = tensor.shard_program(cfg.program(), axis, 2)
         assert not partial and piece.output_types[0].dims[0] == (axis, 2)
+
+
+def test_one_process_runs_the_pieces_on_several_devices(fake_driver):
+    """accy_b200_sharded_*: one session per device, every device gets its piece; checked on the
+    recording fake driver (launches and copies per device), refusals with their reasons."""
+    cfg = configs.mismatch(8, 64)
+    multi = tensor.MultiCuda(cfg.program(), "guess", [0, 1, 2, 3])
+    out = np.zeros(8, np.float32)
+    launches = lib.accy_b200_test_fake_call_count(b"cuLaunchKernel")
+    uploads = lib.accy_b200_test_fake_call_count(b"cuMemcpyHtoDAsync")
+    downloads = lib.accy_b200_test_fake_call_count(b"cuMemcpyDtoHAsync")
+    multi.launch(cfg.make_inputs(), [out])
+    assert lib.accy_b200_test_fake_call_count(b"cuLaunchKernel") - launches == 4            # one piece per device
+    assert lib.accy_b200_test_fake_call_count(b"cuMemcpyHtoDAsync") - uploads == 4 * 3      # frequency block, time, sample
+    assert lib.accy_b200_test_fake_call_count(b"cuMemcpyDtoHAsync") - downloads >= 4        # a block of the result each
+    # wrong sizes are those of the whole program
+    with pytest.raises(tensor.SessionError) as e:
+        multi.launch(cfg.make_inputs(), [np.zeros(2, np.float32)])
+    assert e.value.name == "invalid_buffer" and "32 bytes" in e.value.message
+    multi.deinit()
+    # the summed axis: pieces hold partial sums (two launches each: column-split fold and its combine, or one)
+    partial = tensor.MultiCuda(cfg.program(), "point", [0, 1])
+    partial.launch(cfg.make_inputs(), [out])
+    partial.deinit()
+    for axis, devices, reason in [("guess", [0, 1, 2], "does not divide"), ("nothing", [0, 1], "no value carries")]:
+        with pytest.raises(tensor.SessionError) as e:
+            tensor.MultiCuda(cfg.program(), axis, devices)
+        assert e.value.name == "compile_failed" and reason in e.value.message
+    with pytest.raises(tensor.SessionError) as e:
+        tensor.MultiCuda(configs.softmax_layernorm(8, 32).program(), "col", [0, 1])
+    assert e.value.name == "compile_failed"

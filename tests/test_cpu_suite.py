@@ -695,3 +695,44 @@ def test_one_process_runs_the_pieces_on_several_devices(fake_driver):
     with pytest.raises(tensor.SessionError) as e:
         tensor.MultiCuda(configs.softmax_layernorm(8, 32).program(), "col", [0, 1])
     assert e.value.name == "compile_failed"
+
+
+def test_reference_arm_of_the_bench_runs_without_the_native_library():
+    """`bench.py --impl reference` times the CPU restatement only: it must print one JSON line with
+    the native arm's metric, unit and `config.specs`, and must not map libaccy_b200.so (its inputs
+    come from accy_b200/synthetic.py loaded by file path)."""
+    import subprocess
+    import sys
+    root = ROOT
+    probe = ("import runpy, sys\n"
+             "sys.argv = ['bench.py', '--impl', 'reference', '--small', '--steps', '1', '--warmup', '1']\n"
+             "runpy.run_path(%r, run_name='__main__')\n"
+             "maps = open('/proc/self/maps').read()\n"
+             "print('NATIVE_MAPPED' if 'libaccy_b200' in maps else 'NATIVE_ABSENT', file=sys.stderr)\n"
+             "print('ORACLE_MAPPED' if 'libaccy_oracle' in maps else 'ORACLE_ABSENT', file=sys.stderr)\n") % os.path.join(root, "bench.py")
+    done = subprocess.run([sys.executable, "-c", probe], capture_output=True, text=True, cwd=root, timeout=300)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert "NATIVE_ABSENT" in done.stderr and "ORACLE_MAPPED" in done.stderr
+    line = json.loads(done.stdout.strip().split("\n")[-1])
+    assert line["impl"] == "reference" and line["metric"] == "fused_reduce_hbm_gbs" and line["unit"] == "GB/s"
+    assert line["config"]["workload"] == "softmax_layernorm" and line["config"]["specs"] == ["f32[row=8192, col=4096]"]
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["single_core"]["cores"] == 1
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["gpu_launches"] == 0 and line["value"] > 0
+
+
+def test_synthetic_inputs_are_the_configs_inputs():
+    """accy_b200/synthetic.py (plain numpy, loadable by path) and accy_b200.configs give the same bytes and specs."""
+    import importlib.util
+    path = os.path.join(ROOT, "accy_b200", "synthetic.py")
+    spec = importlib.util.spec_from_file_location("synthetic_by_path", path)
+    synthetic = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(synthetic)
+    for name, cfg in [("mismatch", configs.mismatch(6, 40)), ("softmax_layernorm", configs.softmax_layernorm(4, 8)),
+                      ("matmul", configs.matmul(8, 16, 24)), ("attention", configs.attention(1, 2, 8, 4)), ("mlp", configs.mlp(4, 8, 16))]:
+        sizes = [(n, e) for n, e in synthetic.SIZES[name]]
+        dims = {n: e for s in cfg.specs for n, e in s.dims}
+        sizes = [(n, dims[n]) for n, _ in sizes]
+        assert [synthetic.spec_text(s) for s in synthetic.specs(name, sizes)] == [repr(t) for t in cfg.program().input_types]
+        for a, b in zip(synthetic.inputs(name, sizes), cfg.make_inputs()):
+            assert a.dtype == b.dtype and np.array_equal(a, b)
+        assert synthetic.work(name, sizes) == cfg.work

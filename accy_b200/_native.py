@@ -53,6 +53,7 @@ PROTOTYPES = {
     "accy_b200_session_work": (c_u32, [c_p, c_u64, P(Work)]),
     "accy_b200_session_kernel_count": (c_u32, [c_p, c_u64, P(c_u32)]),
     "accy_b200_session_kernel_source": (c_str, [c_p, c_u64, c_u32, P(c_str), P(c_str)]),
+    "accy_b200_session_time_launches": (c_u32, [c_p, c_u32]),
     "accy_b200_session_last_kernel_ms": (c_u32, [c_p, c_u64, P(ctypes.c_float)]),
     "accy_b200_builder_create": (c_u32, [c_str, P(c_p)]),
     "accy_b200_builder_destroy": (None, [c_p]),

@@ -95,6 +95,7 @@ struct accy_b200_session {
   CUcontext_t context = nullptr;
   CUstream_t stream = nullptr;
   int sm_count = 148;
+  bool time_launches = false;      // accy_b200_session_time_launches
   CUdeviceptr_t status_word = 0;  // device int the tcgen05 kernels set when a bounded wait gives up
 
   void observe(const char* phase, uint64_t begin_ns) {
@@ -391,7 +392,10 @@ struct accy_b200_session {
   void launchAll(Entry& e, CUstream_t on, bool time_it) {
     if (poisoned) throw StatusError{ACCY_B200_LAUNCH_FAILED, "session is poisoned by an earlier failed launch"};
     const DriverTable& d = driver();
-    if (time_it) check(d.cuEventRecord(e.ev_begin, on), "cuEventRecord");
+    // Events around the launch list cost the stream a few microseconds per invoke (each one
+    // drains the kernels before it), so they are recorded only when the caller asked for timings.
+    const bool record_events = time_it && time_launches;
+    if (record_events) check(d.cuEventRecord(e.ev_begin, on), "cuEventRecord");
     static const bool graphs_off = std::getenv("ACCY_B200_NO_GRAPHS") != nullptr;
     const bool replayable = time_it && !graphs_off && e.plan.launches.size() >= 2 && e.graph_recordings < 4;
     bool submitted = false;
@@ -422,7 +426,7 @@ struct accy_b200_session {
       if (recorded) d.cuGraphDestroy(recorded);
     }
     if (!submitted) issueLaunches(e, on);
-    if (time_it) {
+    if (record_events) {
       check(d.cuEventRecord(e.ev_end, on), "cuEventRecord");
       e.timed = true;
     }
@@ -802,10 +806,14 @@ const char* accy_b200_session_kernel_source(accy_b200_session* s, uint64_t handl
   return out;
 }
 
+uint32_t accy_b200_session_time_launches(accy_b200_session* s, uint32_t enable) {
+  return guarded(s, [&] { s->time_launches = enable != 0; });
+}
+
 uint32_t accy_b200_session_last_kernel_ms(accy_b200_session* s, uint64_t handle, float* ms) {
   return guarded(s, [&] {
     Entry& e = s->entryOf(handle);
-    if (!e.timed) throw StatusError{ACCY_B200_LAUNCH_FAILED, "no timed launch yet"};
+    if (!e.timed) throw StatusError{ACCY_B200_LAUNCH_FAILED, "no timed launch yet (timing is switched on by accy_b200_session_time_launches)"};
     const DriverTable& d = driver();
     s->check(d.cuEventSynchronize(e.ev_end), "cuEventSynchronize");
     s->check(d.cuEventElapsedTime(ms, e.ev_begin, e.ev_end), "cuEventElapsedTime");

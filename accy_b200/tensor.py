@@ -540,6 +540,11 @@ class Session:
         self._observer = _native.OBSERVER(lambda ctx, phase, ns: fn(phase.decode(), ns)) if fn else _native.OBSERVER()
         self._check(lib.accy_b200_session_set_observer(self._h, self._observer, None))
 
+    def time_launches(self, enable=True):
+        """Record CUDA events around every invoke's kernels, for `Compiled.last_kernel_ms` (off by default:
+        the events cost a stream of back-to-back invokes a few microseconds each)."""
+        self._check(lib.accy_b200_session_time_launches(self._h, 1 if enable else 0))
+
     def compile(self, wire_bytes):
         wire_bytes = wire_bytes.wire if isinstance(wire_bytes, Program) else bytes(wire_bytes)
         handle = ctypes.c_uint64()

@@ -483,42 +483,68 @@ class Runner:
         d_in = [torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).cuda() for a in inputs]
         out_desc = compiled.output_descriptors()
         d_out = [torch.empty(d.byte_size, dtype=torch.uint8, device="cuda") for d in out_desc]
-        in_ptrs = [t.data_ptr() for t in d_in]
-        out_ptrs = [t.data_ptr() for t in d_out]
         stream = self.stream
         io_bytes = sum(t.numel() * t.element_size() for t in d_in) + sum(t.numel() for t in d_out)
-        flush = None
-        if io_bytes < 256 * 1024 * 1024:
+        # No step may find its data in L2 (126 MB).  A step that moves 256 MiB or more cannot; smaller
+        # ones rotate through copies of their buffers that together hold 2.5 times L2; the smallest
+        # (the inputs of mismatch: 0.6 MB, reused thousands of times inside one launch anyway) have a
+        # 256 MiB buffer written between steps instead, which needs one pair of events per step.
+        flush, n_sets = None, 1
+        if io_bytes < 16 * 1024 * 1024:
             if self.flush is None:
                 self.flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
             flush = self.flush
+            l2_rule = "flushed between steps"
+        elif io_bytes < 256 * 1024 * 1024:
+            n_sets = int(np.ceil(2.5 * 126e6 / io_bytes))
+            l2_rule = "%d buffer sets in rotation, larger than L2 together" % n_sets
+        else:
+            l2_rule = "inputs larger than L2"
+        in_sets = [d_in] + [[t.clone() for t in d_in] for _ in range(n_sets - 1)]
+        out_sets = [d_out] + [[torch.empty_like(t) for t in d_out] for _ in range(n_sets - 1)]
+        in_ptrs = [[t.data_ptr() for t in ts] for ts in in_sets]
+        out_ptrs = [[t.data_ptr() for t in ts] for ts in out_sets]
 
-        def step():
-            session.invoke_device(compiled, in_ptrs, out_ptrs, stream.cuda_stream)
+        def step(i=0):
+            session.invoke_device(compiled, in_ptrs[i % n_sets], out_ptrs[i % n_sets], stream.cuda_stream)
 
         warmup = max(warmup, 3)
-        for _ in range(warmup):
+        for i in range(warmup):
             if flush is not None:
                 flush.zero_()
-            step()
+            step(i)
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         load_t0 = time.perf_counter()   # clock samples count from here: the GPU is under load until load_t1
         wall0 = time.perf_counter()
-        for i in range(steps):
-            if flush is not None:
+        if flush is not None:
+            for i in range(steps):
                 flush.zero_()
-            starts[i].record(stream)
-            step()
-            ends[i].record(stream)
+                starts[i].record(stream)
+                step(i)
+                ends[i].record(stream)
+        else:
+            # the timed region: the steps back to back between one pair of events
+            first.record(stream)
+            for i in range(steps):
+                step(i)
+            last.record(stream)
         torch.cuda.synchronize()
         wall = time.perf_counter() - wall0
         if world > 1:
             dist.barrier()
+        if flush is None:
+            # once more with a pair of events around every step, for the spread (min, median) only
+            for i in range(steps):
+                starts[i].record(stream)
+                step(i)
+                ends[i].record(stream)
+            torch.cuda.synchronize()
         self.launches += work["launches"] * steps
         clocks = None
         if rank == 0:
@@ -537,7 +563,7 @@ class Runner:
                 load_t1 = time.perf_counter()
             clocks = self.sampler.window(load_t0, load_t1, how)
         step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
-        total_ms = self.max_over_ranks(float(sum(step_ms)))
+        total_ms = self.max_over_ranks(float(sum(step_ms)) if flush is not None else first.elapsed_time(last))
         global_work = synthetic.work(name, global_sizes)
         units = units_per_step(name, global_work)       # of the whole job
         local_work = cfg.work
@@ -590,7 +616,7 @@ class Runner:
 
         record = None
         if rank == 0:
-            avg_ms = float(np.mean(step_ms))
+            avg_ms = total_ms / steps if flush is None else float(np.mean(step_ms))
             note = None
             extra = {}
             if bound == "hbm":
@@ -632,7 +658,7 @@ class Runner:
                 v, cores, sample, _, _ = cpu_sample(name, inputs, 1, budget_s=15.0)
                 cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample}
             config = config_record(name, global_sizes, world, scaling if world > 1 else "weak", args.small,
-                                   "flushed between steps" if flush is not None else "inputs larger than L2")
+                                   l2_rule)
             record = {"piece_specs": [repr(t) for t in program.input_types],
                       "plan": compiled.plan_summary().strip().split("\n"), "metric": metric, "value": value, "unit": unit, "ms_per_step": total_ms / steps, "steps": steps,
                       "warmup": warmup, "dtype": cfg.dtype, "config": config, "roofline": roofline,
@@ -640,7 +666,7 @@ class Runner:
                       "clocks": clocks, "parity": parity, "cpu_baseline": cpu, "e2e": e2e,
                       "gpu_launches": work["launches"] * steps, "wall_ms_per_step": 1e3 * wall / steps}
         session.deinit()
-        del d_in, d_out
+        del d_in, d_out, in_sets, out_sets
         torch.cuda.empty_cache()
         return record
 

@@ -139,7 +139,12 @@ uint32_t accy_b200_session_work(accy_b200_session* session, uint64_t handle, acc
 uint32_t accy_b200_session_kernel_count(accy_b200_session* session, uint64_t handle, uint32_t* count);
 const char* accy_b200_session_kernel_source(accy_b200_session* session, uint64_t handle, uint32_t index,
                                             const char** name, const char** options);
-/* Device time of the most recent invoke's kernels (CUDA events around the launch list), ms. */
+/* Device time of the most recent invoke's kernels, ms (elapsed_event_ns of the device vtable,
+ * deps/lib/compiler/gpu/src/contract.zig:2048-2085).  The two CUDA events around the launch list
+ * are recorded only after accy_b200_session_time_launches(session, 1): in a stream of back-to-back
+ * invokes they cost a few microseconds each, so they are off by default, and last_kernel_ms then
+ * answers LAUNCH_FAILED. */
+uint32_t accy_b200_session_time_launches(accy_b200_session* session, uint32_t enable);
 uint32_t accy_b200_session_last_kernel_ms(accy_b200_session* session, uint64_t handle, float* ms);
 
 /* ---- builder: tensor.define recording (builder.zig, value.zig) ----

@@ -466,6 +466,30 @@ def test_invoke_flow_on_the_fake_driver(fake_driver):
     session.deinit()
 
 
+def test_launch_timing_events_are_recorded_only_on_request(fake_driver):
+    """The two events behind last_kernel_ms cost a stream of back-to-back invokes a few microseconds
+    each, so an invoke records them only after time_launches(True)."""
+    session = tensor.Session(device=0)
+    cfg = configs.mismatch(8, 16)
+    compiled = session.compile(cfg.program())
+    out = np.zeros(8, np.float32)
+    events = lambda: lib.accy_b200_test_fake_call_count(b"cuEventRecord")
+    before = events()
+    session.invoke(compiled, cfg.make_inputs(), [out])
+    assert events() == before
+    with pytest.raises(tensor.SessionError) as e:
+        compiled.last_kernel_ms()
+    assert e.value.name == "launch_failed" and "time_launches" in str(e.value)
+    session.time_launches(True)
+    session.invoke(compiled, cfg.make_inputs(), [out])
+    assert events() == before + 2
+    assert compiled.last_kernel_ms() >= 0.0
+    session.time_launches(False)
+    session.invoke(compiled, cfg.make_inputs(), [out])
+    assert events() == before + 2
+    session.deinit()
+
+
 def test_multi_kernel_programs_replay_a_recorded_launch_sequence(fake_driver):
     """A plan of several kernels is captured as a CUDA graph by its first host invoke and replayed
     by the following ones: the kernels are enqueued once, later invokes submit the graph only."""

@@ -626,6 +626,13 @@ class Runner:
                 achieved = local_work["flops"] / 1e12 / (avg_ms / 1e3)
                 peak, peak_unit = self.peaks["bf16_tflops"], "TFLOP/s"
                 extra["peak_sustained"] = self.peaks["bf16_tflops_sustained"]
+                # These kernels run at the 1000 W power cap, where the SM clock (sampled below) settles
+                # well under its maximum: the same achieved rate against what the tensor pipes can do at
+                # that clock (8192 dense bf16 flop per clock per SM: eight 128x128x16 MMAs take 512 cycles)
+                mhz = (clocks or {}).get("sm_mhz")
+                if mhz:
+                    at_clock = 148 * 8192 * mhz * 1e6 / 1e12
+                    extra["at_sampled_clock"] = {"sm_mhz": mhz, "tensor_peak": at_clock, "frac": achieved / at_clock}
             else:
                 # FP32-bound: (guess, point) pairs per second against what a register-only loop of
                 # CUDA's sinf plus the program's four other operations reaches on this GPU, and the

@@ -205,6 +205,7 @@ uint32_t accy_b200_sharded_invoke(accy_b200_sharded* s, uint64_t handle, const v
   std::vector<std::thread> threads;
   for (size_t d = 0; d < devices; ++d) {
     threads.emplace_back([&, d] {
+     try {
       std::vector<const void*> in(input_count);
       std::vector<size_t> in_size(input_count);
       std::vector<void*> out(output_count);
@@ -232,6 +233,13 @@ uint32_t accy_b200_sharded_invoke(accy_b200_sharded* s, uint64_t handle, const v
       status[d] = accy_b200_session_invoke(s->sessions[d], e->handles[d], in.data(), in_size.data(), input_count, out.data(),
                                            out_size.data(), output_count);
       if (status[d] != ACCY_B200_OK) message[d] = accy_b200_session_last_error(s->sessions[d]);
+     } catch (const std::bad_alloc&) {
+      status[d] = ACCY_B200_OUT_OF_MEMORY;
+      message[d] = "out of host memory for the partial results";
+     } catch (const std::exception& err) {
+      status[d] = ACCY_B200_LAUNCH_FAILED;
+      message[d] = err.what();
+     }
     });
   }
   for (std::thread& t : threads) t.join();

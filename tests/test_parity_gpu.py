@@ -398,6 +398,34 @@ def test_resident_inputs_give_the_same_bytes(gpu_session, make, kept):
     gpu_session.release(compiled)
 
 
+def test_launch_timing_is_off_until_asked_for():
+    """last_kernel_ms (the device vtable's elapsed_event_ns, deps/lib/compiler/gpu/src/contract.zig:2048-2085)
+    answers only after time_launches(True); the measured time of a 268 MB row program lies between what
+    HBM allows and a millisecond, and the result bytes do not depend on the switch."""
+    session = tensor.Session(device=0)
+    cfg = configs.softmax_layernorm(8192, 4096)
+    inputs = cfg.make_inputs()
+    compiled = session.compile(cfg.program())
+    plain = np.empty(compiled.output_descriptors()[0].byte_size, np.uint8)
+    session.invoke(compiled, inputs, [plain])
+    with pytest.raises(tensor.SessionError) as e:
+        compiled.last_kernel_ms()
+    assert e.value.name == "launch_failed"
+    session.time_launches(True)
+    timed = np.zeros_like(plain)
+    session.invoke(compiled, inputs, [timed])
+    assert np.array_equal(plain, timed)
+    import torch
+    x = torch.from_numpy(inputs[0]).cuda()
+    out = torch.empty(plain.size, dtype=torch.uint8, device="cuda")
+    session.invoke_device(compiled, [x.data_ptr()], [out.data_ptr()])
+    session.synchronize()
+    ms = compiled.last_kernel_ms()
+    assert 0.03 < ms < 1.0, ms
+    assert np.array_equal(out.cpu().numpy(), plain)
+    session.deinit()
+
+
 @pytest.mark.parametrize("make", [lambda: configs.softmax_layernorm(8192, 4096), lambda: configs.mlp(4096, 2048, 4096),
                                   lambda: configs.attention(8, 4, 1024, 128)])
 def test_chunked_host_invoke_equals_single_shot(make):

@@ -194,3 +194,33 @@ def test_mlp_full_size_sampled_tokens(gpu_session):
     assert rel_err_bf16(got[rows.astype(np.int64)], want) < 2e-2
     mean_square = (got.astype(np.float64) ** 2).mean(axis=1)
     assert np.all(np.abs(mean_square - 1.0) < 2e-2)
+
+
+@pytest.mark.parametrize("make", [lambda: configs.matmul(2304, 1024, 2048),          # nine tile pairs, 32 k-blocks each
+                                  lambda: configs.matmul(1000, 1032, 264),           # ragged in m, n and k
+                                  lambda: configs.attention(1, 37, 2048, 128, True), # 296 work items on 148 CTAs
+                                  lambda: configs.mlp(1024, 1024, 2048)])
+def test_repeated_device_launches_give_identical_bytes(make):
+    """The tensor-core kernels keep state between launches of one compiled program (stage-ring and
+    accumulator phases, the work counter of the persistent attention kernel) and run with whatever
+    timing the GPU gives them: twenty back-to-back launches on device buffers, each into a cleared
+    output, give the bytes of the first."""
+    import torch
+    cfg = make()
+    inputs = cfg.make_inputs()
+    session = tensor.Session(device=0)
+    compiled = session.compile(cfg.program())
+    d_in = [torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).cuda() for a in inputs]
+    nbytes = compiled.output_descriptors()[0].byte_size
+    first = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    outs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(20)]
+    torch.cuda.synchronize()   # the session launches on a stream of its own
+    session.invoke_device(compiled, [t.data_ptr() for t in d_in], [first.data_ptr()])
+    session.synchronize()
+    assert first.any()
+    for out in outs:
+        session.invoke_device(compiled, [t.data_ptr() for t in d_in], [out.data_ptr()])
+    session.synchronize()
+    for out in outs:
+        assert torch.equal(out, first)
+    session.deinit()

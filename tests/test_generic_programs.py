@@ -186,3 +186,76 @@ def test_zero_extent_programs_match_oracle(gpu_session, name):
     expected = oracle.run(program.wire, inputs, mode="ref")
     for got, want in zip(outs, expected):
         assert np.array_equal(got.view(np.float32), np.asarray(want, np.float32).reshape(-1))
+
+
+def random_sum_program(seed):
+    """A seeded random f32 program over [r, c] with sums, means, maxima and softmax-like groups over c,
+    over r or over both, broadcast back by name: (specs, body, inputs).  All values stay positive, so
+    no sum cancels and a relative tolerance means something for every element."""
+    rng = np.random.default_rng(9000 + seed)
+    r = int(rng.choice([1, 4, 48, 300]))
+    c = int(rng.choice([1, 9, 256, 1000, 6000]))
+    kinds = ["full", "full", str(rng.choice(["row", "col"]))]
+    specs, inputs = [], []
+    for kind in kinds:
+        shape = {"full": (r, c), "row": (r,), "col": (c,)}[kind]
+        specs.append(T.spec("f32", **({"r": r, "c": c} if kind == "full" else ({"r": r} if kind == "row" else {"c": c}))))
+        inputs.append(rng.uniform(0.25, 2.0, shape).astype(np.float32))
+    dims_of = [{"full": ("r", "c"), "row": ("r",), "col": ("c",)}[k] for k in kinds]
+    steps = []
+    for _ in range(int(rng.integers(4, 9))):
+        op = str(rng.choice(["add", "mul", "div", "max", "min", "sqrt", "scale", "reduce", "reduce", "softmax"]))
+        picks = [int(p) for p in rng.integers(0, len(dims_of), 2)]
+        how = (str(rng.choice(["sum", "mean", "max"])), str(rng.choice(["c", "r", "rc"])), float(np.float32(rng.uniform(0.25, 1.5))))
+        if op in ("reduce", "softmax"):
+            have = dims_of[picks[0]]
+            axes = tuple(a for a in how[1] if a in have)
+            if not axes:
+                op = "sqrt"
+                dims_of.append(have)
+            else:
+                how = (how[0], axes, how[2])
+                dims_of.append(have if op == "softmax" else tuple(a for a in have if a not in axes))
+        elif op in ("sqrt", "scale"):
+            dims_of.append(dims_of[picks[0]])
+        else:
+            dims_of.append(tuple(a for a in ("r", "c") if a in dims_of[picks[0]] or a in dims_of[picks[1]]))
+        steps.append((op, picks, how))
+
+    def body(b, a):
+        values = list(a)
+        for op, p, how in steps:
+            x, y = values[p[0]], values[p[1]]
+            if op in ("add", "mul", "div", "max", "min"):
+                v = getattr(x, op)(y)
+            elif op == "sqrt":
+                v = x.sqrt()
+            elif op == "scale":
+                v = x.mul(b.scalar("f32", how[2]))
+            elif op == "reduce":
+                v = getattr(x, how[0])(list(how[1]))
+            else:   # exp(x - max) / sum(exp(x - max)) over the axes, shifted so that it stays positive
+                e = x.sub(x.max(list(how[1]))).exp()
+                v = e.div(e.sum(list(how[1]))).add(b.scalar("f32", 0.125))
+            values.append(v)
+        out = values[-1]
+        for v in a:
+            out = out.add(v)
+        return out
+
+    return specs, body, inputs
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(20))
+def test_random_programs_with_sums_match_oracle(gpu_session, seed):
+    specs, body, inputs = random_sum_program(seed)
+    program = tensor.define("random_sums_%d" % seed, specs, body)
+    compiled = gpu_session.compile(program)
+    out = np.empty(compiled.output_descriptors()[0].byte_size, np.uint8)
+    gpu_session.invoke(compiled, inputs, [out])
+    gpu_session.release(compiled)
+    ref = np.asarray(oracle.run(program.wire, inputs, mode="ref")[0], np.float64).reshape(-1)
+    exact = np.asarray(oracle.run(program.wire, inputs, mode="f64")[0], np.float64).reshape(-1)
+    assert np.isfinite(exact).all()
+    check_three_distances("random_sums_%d" % seed, out.view(np.float32).astype(np.float64), ref, exact, 1e-6)

@@ -224,3 +224,56 @@ def test_repeated_device_launches_give_identical_bytes(make):
     for out in outs:
         assert torch.equal(out, first)
     session.deinit()
+
+
+def random_gemm(seed):
+    """A seeded random bf16 contraction: extents from 1 to about 700 (multiples of eight and not),
+    either operand stored either way round, an optional leading batch axis, an optional epilogue
+    (bias, bias + tanh, scale, bias added to a product with a second matrix): (specs, body)."""
+    rng = np.random.default_rng(7000 + seed)
+    def extent():
+        e = int(rng.integers(1, 700))
+        return e if rng.random() < 0.4 else max(8, e // 8 * 8)
+    m, n, k = extent(), extent(), extent()
+    g = int(rng.choice([0, 0, 2, 3]))
+    lhs = [("m", m), ("k", k)] if rng.random() < 0.6 else [("k", k), ("m", m)]
+    rhs = [("k", k), ("n", n)] if rng.random() < 0.6 else [("n", n), ("k", k)]
+    if g:
+        lhs, rhs = [("g", g)] + lhs, [("g", g)] + rhs
+    epilogue = str(rng.choice(["none", "bias", "bias_tanh", "scale", "residual"]))
+    specs = [tensor.spec("bf16", **dict(lhs)), tensor.spec("bf16", **dict(rhs))]
+    if epilogue in ("bias", "bias_tanh"):
+        specs.append(tensor.spec("bf16", n=n))
+    if epilogue == "residual":
+        specs.append(tensor.spec("bf16", **dict(([("g", g)] if g else []) + [("m", m), ("n", n)])))
+
+    def body(b, a):
+        y = a[0].contract(a[1], "k")
+        if epilogue == "bias":
+            y = y.add(a[2])
+        elif epilogue == "bias_tanh":
+            y = y.add(a[2]).tanh()
+        elif epilogue == "scale":
+            y = y.mul(b.scalar("bf16", 0.5))
+        elif epilogue == "residual":
+            y = y.add(a[2])
+        return y
+
+    return specs, body, "m%d n%d k%d g%d %s %s %s" % (m, n, k, g, "".join(d for d, _ in lhs), "".join(d for d, _ in rhs), epilogue)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_bf16_contractions_match_the_oracle(gpu_session, seed):
+    """Whatever kernel the planner picks for the shape (the two-CTA or the one-CTA tcgen05 kernel, or the
+    exact-order SIMT kernel where a TMA rule keeps the tensor cores out), the result matches the f32
+    evaluation on the bf16-rounded inputs and nothing behind the output is written."""
+    specs, body, label = random_gemm(seed)
+    program = tensor.define("random_gemm_%d" % seed, specs, body)
+    rng = np.random.default_rng(seed)
+    inputs = [bf16(rng.standard_normal([e for _, e in sp.dims]) / 4.0) for sp in specs]
+    out, summary = run(gpu_session, program, inputs)
+    want = widen(oracle.run(program.wire, inputs, mode="wide")[0]).reshape(-1)
+    got = widen(out.view(np.uint16))
+    err = rel_err_bf16(got, want)
+    print(label, "->", "tcgen05" if "accy_gemm_tc" in summary else "simt", "err %.3g" % err)
+    assert err < 2e-2, (label, err)

@@ -298,6 +298,43 @@ def test_cross_attention_key_lengths(gpu_session, seq, keys):
     assert rel_err_bf16(got, ref) < 2e-2
 
 
+def random_attention(seed):
+    """seeded random attention shapes: (batch, heads, queries, head dim, causal, keys)"""
+    rng = np.random.default_rng(3000 + seed)
+    causal = bool(rng.random() < 0.5)
+    dim = int(rng.choice([64, 128]))
+    batch, heads = int(rng.integers(1, 3)), int(rng.integers(1, 4))
+    seq = int(rng.integers(128, 900))
+    if rng.random() < 0.5:
+        seq = seq // 128 * 128
+    keys = None
+    if not causal and rng.random() < 0.6:
+        keys = int(rng.integers(128, 900))
+    return batch, heads, seq, dim, causal, keys
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_attention_shapes_match_the_oracle(gpu_session, seed):
+    """Query and key lengths that are and are not multiples of the 128-row tiles and 128-key blocks, both
+    head dims, causal and not, cross attention: the fused kernel against the f32 SDPA restatement."""
+    batch, heads, seq, dim, causal, keys = random_attention(seed)
+    cfg = configs.attention(batch, heads, seq, dim, causal, keys=keys, seed=100 + seed)
+    inputs = cfg.make_inputs()
+    program = cfg.program()
+    compiled = gpu_session.compile(program)
+    assert "attention:" in compiled.plan_summary()
+    size = compiled.output_descriptors()[0].byte_size
+    out = np.full(size + 4096, 0x5A, np.uint8)
+    gpu_session.invoke(compiled, inputs, [out[:size]])
+    gpu_session.release(compiled)
+    assert np.all(out[size:] == 0x5A)
+    got = configs.bf16_bits_to_f32(out[:size].view(np.uint16))
+    ref = configs.bf16_bits_to_f32(oracle.run(program.wire, inputs, mode="wide")[0]).reshape(-1)
+    err = rel_err_bf16(got, ref)
+    print("batch %d heads %d queries %d dim %d causal %s keys %s: err %.3g" % (batch, heads, seq, dim, causal, keys, err))
+    assert err < 2e-2
+
+
 def test_attention_repeated_launches_agree(gpu_session):
     """The persistent attention kernel hands out work through a device counter that every launch
     must leave cleared: three launches of one compiled program give the same bytes."""

@@ -259,3 +259,31 @@ def test_random_programs_with_sums_match_oracle(gpu_session, seed):
     exact = np.asarray(oracle.run(program.wire, inputs, mode="f64")[0], np.float64).reshape(-1)
     assert np.isfinite(exact).all()
     check_three_distances("random_sums_%d" % seed, out.view(np.float32).astype(np.float64), ref, exact, 1e-6)
+
+
+def test_schedules_of_folds_over_a_leading_axis_and_of_flat_programs(cpu_session):
+    """A fold over a leading axis of a row-major buffer runs with one thread per kept column (256
+    neighbouring columns per CTA, the folded axis cut into slices); an elementwise-only flat program gets
+    one chunk per CTA; the many partials of a one-row fold are combined by a warp."""
+    def plan(name, specs, body):
+        compiled = cpu_session.compile(tensor.define(name, specs, body))
+        summary, kernels = compiled.plan_summary(), {n: src for n, src, _ in compiled.kernels()}
+        cpu_session.release(compiled)
+        return summary, kernels
+    summary, _ = plan("column_sums", [T.spec("f32", r=16384, c=4096)], lambda b, a: a[0].sum("r"))
+    assert "rows=4096 cols=16384" in summary and "tpr=1 rpc=256" in summary and "splits=64" in summary
+    summary, _ = plan("interior_sums", [T.spec("f32", a=256, b=256, c=1024)], lambda b, a: a[0].sum("b"))
+    assert "tpr=1 rpc=256" in summary
+    # the same fold over the trailing axis keeps 256 threads on a row
+    summary, _ = plan("row_sums", [T.spec("f32", r=16384, c=4096)], lambda b, a: a[0].sum("c"))
+    assert "tpr=256" in summary and "splits=1 " in summary
+    summary, _ = plan("flat", [T.spec("f32", n=1 << 26)] * 3, lambda b, a: a[0].mul(a[1]).add(a[2]))
+    assert "chunks=16384 splits=16384" in summary
+    summary, kernels = plan("total", [T.spec("f32", n=1 << 26)], lambda b, a: a[0].mul(a[0]).sum("n"))
+    assert "splits=863" in summary
+    combine = [src for n, src in kernels.items() if n.endswith("_combine")]
+    assert len(combine) == 1 and "__shfl_xor_sync" in combine[0].split("extern \"C\"")[-1]
+    # few partials per row: one thread per row folds them in order
+    _, kernels = plan("few_partials", [T.spec("f32", r=16, c=1 << 16)], lambda b, a: a[0].sum("c"))
+    combine = [src for n, src in kernels.items() if n.endswith("_combine")]
+    assert len(combine) == 1 and "__shfl_xor_sync" not in combine[0].split("extern \"C\"")[-1]

@@ -287,3 +287,20 @@ def test_schedules_of_folds_over_a_leading_axis_and_of_flat_programs(cpu_session
     _, kernels = plan("few_partials", [T.spec("f32", r=16, c=1 << 16)], lambda b, a: a[0].sum("c"))
     combine = [src for n, src in kernels.items() if n.endswith("_combine")]
     assert len(combine) == 1 and "__shfl_xor_sync" not in combine[0].split("extern \"C\"")[-1]
+
+
+def test_a_fold_over_a_leading_axis_that_is_used_further_gets_its_own_kernel(cpu_session):
+    """Centring over axis 0: the column means come from a kernel of their own (one thread per column)
+    and the subtraction runs along the rows; the same program over axis 1 stays one fused row kernel;
+    two column folds that are both outputs still share one pass over the input."""
+    def kernels_of(name, specs, body):
+        compiled = cpu_session.compile(tensor.define(name, specs, body))
+        lines = [l.strip() for l in compiled.plan_summary().strip().split("\n") if l.strip().startswith("row kernel")]
+        cpu_session.release(compiled)
+        return lines
+    lines = kernels_of("centre_columns", [T.spec("f32", r=8192, c=8192)], lambda b, a: a[0].sub(a[0].mean("r")))
+    assert len(lines) == 2 and "reduces=1 tpr=1 rpc=256" in lines[0] and "reduces=0 tpr=256" in lines[1] and "vec=4" in lines[1]
+    lines = kernels_of("centre_rows", [T.spec("f32", r=8192, c=8192)], lambda b, a: a[0].sub(a[0].mean("c")))
+    assert len(lines) == 1 and "reduces=1 tpr=256" in lines[0]
+    lines = kernels_of("two_column_folds", [T.spec("f32", r=8192, c=8192)], lambda b, a: [a[0].sum("r"), a[0].mul(a[0]).sum("r")])
+    assert len(lines) == 1 and "reduces=2 tpr=1 rpc=256" in lines[0] and "outputs=2" in lines[0]

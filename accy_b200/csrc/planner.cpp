@@ -47,7 +47,33 @@ class Planner {
       for (uint32_t a : op.operands) users[a].push_back(op.id);
     is_output.assign(P.ops.size(), false);
     for (uint32_t id : P.outputs) is_output[id] = true;
+    // Value numbering: an operation that repeats an earlier one (same kind, attributes, result type and
+    // the same operands up to this relation) stands for it.  Inside a fused region repeated
+    // subexpressions already collapse node by node; this is for values that become kernels of their
+    // own, so that x.max(r) written out twice is one fold, not two.
+    same_as.resize(P.ops.size());
+    std::map<std::string, uint32_t> seen;
+    for (const Operation& op : P.ops) {
+      same_as[op.id] = op.id;
+      if (op.kind == Kind::parameter) continue;
+      std::string key;
+      auto put = [&](int64_t x) { key.append(reinterpret_cast<const char*>(&x), sizeof(x)); };
+      put(static_cast<int64_t>(op.kind)); put(op.sub); put(static_cast<int64_t>(op.result.dtype)); put(static_cast<int64_t>(op.result.rank()));
+      for (const Dim& d : op.result.dims) { key += d.name; key.push_back('\0'); put(d.extent); }
+      put(static_cast<int64_t>(op.operands.size()));
+      for (uint32_t a : op.operands) put(same_as[a]);
+      for (const std::vector<int64_t>* list : {&op.ints, &op.rhs_contract, &op.lhs_batch, &op.rhs_batch}) {
+        put(static_cast<int64_t>(list->size()));
+        for (int64_t x : *list) put(x);
+      }
+      put(op.axis); put(static_cast<int64_t>(op.index)); put(op.version);
+      key += op.target; key.push_back('\0');
+      key.append(reinterpret_cast<const char*>(op.payload.data()), op.payload.size());
+      auto found = seen.emplace(key, op.id);
+      if (!found.second) same_as[op.id] = found.first->second;
+    }
   }
+  std::vector<uint32_t> same_as;   // the earliest operation computing the same value
 
   Plan run() {
     plan.input_slots.resize(P.parameters.size());
@@ -156,6 +182,12 @@ class Planner {
   // Ensures v lives in a device buffer laid out row-major in its own dims; returns the slot.
   int materialize(uint32_t v) {
     if (slot_of[v] >= 0) return slot_of[v];
+    if (same_as[v] != v && !is_output[v] && narrow.count(v) == narrow.count(same_as[v])) {
+      // the same value was (or is now) computed under an earlier name: read that buffer
+      const int s = materialize(same_as[v]);
+      slot_of[v] = s;
+      return s;
+    }
     const Operation& op = P.ops[v];
     switch (op.kind) {
       case Kind::constant: {

@@ -304,3 +304,18 @@ def test_a_fold_over_a_leading_axis_that_is_used_further_gets_its_own_kernel(cpu
     assert len(lines) == 1 and "reduces=1 tpr=256" in lines[0]
     lines = kernels_of("two_column_folds", [T.spec("f32", r=8192, c=8192)], lambda b, a: [a[0].sum("r"), a[0].mul(a[0]).sum("r")])
     assert len(lines) == 1 and "reduces=2 tpr=1 rpc=256" in lines[0] and "outputs=2" in lines[0]
+
+
+def test_a_value_recorded_twice_is_computed_once(cpu_session):
+    """x.max(r) written out for two uses is one fold kernel, and a contraction recorded twice is one GEMM."""
+    def kernels_of(name, specs, body):
+        compiled = cpu_session.compile(tensor.define(name, specs, body))
+        lines = [l.strip() for l in compiled.plan_summary().strip().split("\n") if l.strip().startswith(("row kernel", "gemm"))]
+        cpu_session.release(compiled)
+        return lines
+    lines = kernels_of("softmax_over_axis_0", [T.spec("f32", r=4096, c=4096)],
+                       lambda b, a: a[0].sub(a[0].max("r")).exp().div(a[0].sub(a[0].max("r")).exp().sum("r")))
+    assert len(lines) == 3 and sum("reduces=1" in l for l in lines) == 2
+    lines = kernels_of("same_product_twice", [T.spec("bf16", m=256, k=256), T.spec("bf16", k=256, n=256)],
+                       lambda b, a: a[0].contract(a[1], "k").add(a[0].contract(a[1], "k")))
+    assert sum(l.startswith("gemm") for l in lines) == 1

@@ -1197,6 +1197,25 @@ class Planner {
 // The same pass brings every contraction to the operand order the kernels take (the reference's
 // dot lowering accepts only that order, dot.zig:2117-2161; gradients of contractions produce the
 // others): the operands are transposed, which costs nothing when the strides still describe them.
+// A fold over the innermost axis and at least one more (the sum over rows and columns at the end of a
+// loss): planned as recorded it cannot join the row kernel that computes its operand (whose rows are the
+// innermost axis alone), so the operand's inputs would be read once more.  Folding the innermost axis
+// first and the rest in a second, small step changes only the association of the fold, which the
+// kernels' tree-shaped folds change anyway.  Innermost extents below 64 stay as recorded.
+static bool foldsInTwoStages(const Program& p, const Operation& op) {
+  const Type& in = p.typeOf(op.operands[0]);
+  long innermost = -1;
+  for (size_t i = 0; i < in.rank(); ++i)
+    if (in.dims[i].extent != 1) innermost = static_cast<long>(i);
+  if (innermost < 0 || in.dims[innermost].extent < 64) return false;
+  bool inner_reduced = false, other_reduced = false;
+  for (int64_t d : op.ints) {
+    if (d == innermost) inner_reduced = true;
+    else if (in.dims[d].extent != 1) other_reduced = true;
+  }
+  return inner_reduced && other_reduced;
+}
+
 static Program withoutEmptyFolds(const Program& p) {
   Builder b(p.name);
   std::vector<uint32_t> now(p.ops.size(), 0);
@@ -1222,7 +1241,20 @@ static Program withoutEmptyFolds(const Program& p) {
       case Kind::transpose: made = b.transposeBy(arg(0), op.ints); break;
       case Kind::reduce:
         if (!empty && p.typeOf(op.operands[0]).elementCount() == 0) made = b.broadcastTo(arg(1), op.result.dims, {});
-        else made = b.reduce(arg(0), arg(1), static_cast<Reducer>(op.sub), op.ints);
+        else if (foldsInTwoStages(p, op)) {
+          // innermost axis first (from the reducer's identity), then the other axes from the recorded
+          // start value: the first stage can share a row kernel with whatever its operand computes
+          // along that axis
+          const Type& in = p.typeOf(op.operands[0]);
+          long innermost = -1;
+          for (size_t i = 0; i < in.rank(); ++i)
+            if (in.dims[i].extent != 1) innermost = static_cast<long>(i);
+          const uint32_t rows = b.reduceNamed(arg(0), static_cast<Reducer>(op.sub), {in.dims[innermost].name});
+          std::vector<int64_t> rest;
+          for (int64_t d : op.ints)
+            if (d != innermost) rest.push_back(d > innermost ? d - 1 : d);
+          made = b.reduce(rows, arg(1), static_cast<Reducer>(op.sub), rest);
+        } else made = b.reduce(arg(0), arg(1), static_cast<Reducer>(op.sub), op.ints);
         break;
       case Kind::dot_general:
         if (!empty && (p.typeOf(op.operands[0]).elementCount() == 0 || p.typeOf(op.operands[1]).elementCount() == 0)) {
@@ -1281,6 +1313,7 @@ Plan planProgram(const Program& program, const ScheduleOverrides& overrides) {
   bool reorder = false;
   for (const Operation& op : program.ops) {
     reorder |= op.kind == Kind::broadcast;
+    reorder |= op.kind == Kind::reduce && foldsInTwoStages(program, op);
     if (op.kind != Kind::dot_general) continue;
     const size_t nb = op.lhs_batch.size(), nk = op.ints.size();
     const size_t nm = program.typeOf(op.operands[0]).rank() - nb - nk;

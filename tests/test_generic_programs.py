@@ -319,3 +319,26 @@ def test_a_value_recorded_twice_is_computed_once(cpu_session):
     lines = kernels_of("same_product_twice", [T.spec("bf16", m=256, k=256), T.spec("bf16", k=256, n=256)],
                        lambda b, a: a[0].contract(a[1], "k").add(a[0].contract(a[1], "k")))
     assert sum(l.startswith("gemm") for l in lines) == 1
+
+
+def test_a_fold_over_rows_and_columns_joins_the_row_kernel_of_its_operand(cpu_session):
+    """The sum over both axes at the end of a layer-norm loss is taken along the rows first: the row means,
+    the row variances and the rows' shares of the loss come out of one kernel that reads the inputs once;
+    a second, small kernel adds up the 8192 shares."""
+    def loss(b, a):
+        x, gain, target = a
+        centred = x.sub(x.mean("c"))
+        y = centred.div(centred.mul(centred).mean("c").add(b.scalar("f32", 1e-5)).sqrt()).mul(gain)
+        d = y.sub(target)
+        return d.mul(d).sum(["r", "c"])
+    specs = [T.spec("f32", r=8192, c=4096), T.spec("f32", c=4096), T.spec("f32", r=8192, c=4096)]
+    compiled = cpu_session.compile(tensor.define("layer_norm_loss", specs, loss))
+    lines = [l.strip() for l in compiled.plan_summary().strip().split("\n") if l.strip().startswith("row kernel")]
+    cpu_session.release(compiled)
+    assert len(lines) == 2
+    assert "rows=8192 cols=4096 reduces=3" in lines[0] and "rows=1 cols=8192 reduces=1" in lines[1]
+    # innermost extents below 64 are folded as recorded
+    compiled = cpu_session.compile(tensor.define("narrow", [T.spec("f32", r=4096, c=8)], lambda b, a: a[0].sum(["r", "c"])))
+    lines = [l.strip() for l in compiled.plan_summary().strip().split("\n") if l.strip().startswith("row kernel")]
+    cpu_session.release(compiled)
+    assert len(lines) == 1 and "cols=32768" in lines[0]

@@ -74,6 +74,12 @@ class Planner {
     }
   }
   std::vector<uint32_t> same_as;   // the earliest operation computing the same value
+  // Values (by their same_as representative) that a first, discarded planning pass gave a region of
+  // their own although they are not outputs: row statistics that a fold over another axis reads, for
+  // instance.  In the second pass a region that computes such a value on its way writes it out as well,
+  // so that it is not computed again from the inputs.
+  std::set<uint32_t> wanted;
+  std::set<uint32_t> standalone;
 
   Plan run() {
     plan.input_slots.resize(P.parameters.size());
@@ -105,9 +111,14 @@ class Planner {
       if (!first_output.count(P.outputs[j])) first_output[P.outputs[j]] = plan.output_slots[j];
     }
     out_slot_of = first_output;
+    // the largest outputs first (a region that computes a large result passes the smaller values the
+    // other outputs need on its way), later operations before earlier ones among equals
     std::vector<uint32_t> roots;
     for (auto& kv : first_output) roots.push_back(kv.first);
-    std::sort(roots.rbegin(), roots.rend());
+    std::sort(roots.begin(), roots.end(), [&](uint32_t a, uint32_t b) {
+      const size_t na = P.typeOf(a).elementCount(), nb = P.typeOf(b).elementCount();
+      return na != nb ? na > nb : a > b;
+    });
     for (uint32_t v : roots) {
       if (produced.count(v)) continue;
       if (P.typeOf(v).elementCount() == 0) {   // nothing to compute
@@ -407,7 +418,7 @@ class Planner {
           }
         }
         if (id < 0) id = addNode(b, n);
-        if (is_output[v] && v != b.root && !produced.count(v)) b.coproduce.push_back({v, id});
+        if ((is_output[v] || wanted.count(same_as[v])) && v != b.root && !produced.count(v)) b.coproduce.push_back({v, id});
         return id;
       }
       case Kind::broadcast_in_dim: {
@@ -536,7 +547,7 @@ class Planner {
     n.level = b.nodes[n.args[0]].level + 1;
     b.closure.insert(v);
     int id = addNode(b, n);
-    if (is_output[v] && v != b.root && !produced.count(v)) b.coproduce.push_back({v, id});
+    if ((is_output[v] || wanted.count(same_as[v])) && v != b.root && !produced.count(v)) b.coproduce.push_back({v, id});
     return id;
   }
 
@@ -546,6 +557,7 @@ class Planner {
   int cluster_depth = 0;  // nesting of planCluster calls (a region materialising what it reads)
 
   void planCluster(uint32_t v) {
+    if (!is_output[v]) standalone.insert(same_as[v]);
     Build b;
     b.root = v;
     const Type& ty = P.typeOf(v);
@@ -1322,13 +1334,22 @@ Plan planProgram(const Program& program, const ScheduleOverrides& overrides) {
     for (size_t i = 0; i < nk; ++i)
       reorder |= op.ints[i] != static_cast<int64_t>(nb + nm + i) || op.rhs_contract[i] != static_cast<int64_t>(nb + i);
   }
+  auto plan_twice = [&](const Program& q) {
+    std::set<uint32_t> wanted;
+    {
+      Planner first(q, overrides);
+      first.run();
+      wanted = first.standalone;
+    }
+    Planner planner(q, overrides);
+    planner.wanted = wanted;
+    return planner.run();
+  };
   if (has_empty || reorder) {
     const Program rewritten = withoutEmptyFolds(program);
-    Planner planner(rewritten, overrides);
-    return planner.run();
+    return plan_twice(rewritten);
   }
-  Planner planner(program, overrides);
-  return planner.run();
+  return plan_twice(program);
 }
 
 }  // namespace accy

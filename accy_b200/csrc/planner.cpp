@@ -593,6 +593,32 @@ class Planner {
       for (auto& cand : b.coproduce) listed = listed || cand.first == u;
       if (!listed) b.coproduce.push_back({u, node});
     }
+    // Folds over this region's columns that another region needs (found by the first planning pass) and
+    // whose operand has the root's dims join as well: the rows' shares of a loss next to the gradient
+    // computed from the same rows, for instance.
+    if (cluster_depth == 1 && b.cols_fixed) {
+      for (uint32_t u : wanted) {
+        if (u == v || produced.count(u) || slot_of[u] >= 0 || b.closure.count(u) || b.nodes.size() > 4000) continue;
+        const Operation& uop = P.ops[u];
+        if (uop.kind != Kind::reduce || !sameDims(P.typeOf(uop.operands[0]).dims, ty.dims)) continue;
+        // it must fold exactly the column dims (those of extent 1 do not matter either way)
+        bool same_axes = true;
+        std::vector<int> umap;
+        for (size_t d = 0; d < ty.rank(); ++d) {
+          const bool folded = std::find(uop.ints.begin(), uop.ints.end(), static_cast<int64_t>(d)) != uop.ints.end();
+          if (ty.dims[d].extent != 1 && folded != static_cast<bool>(b.is_col[d])) same_axes = false;
+          if (!folded) umap.push_back(static_cast<int>(d));
+        }
+        if (!same_axes) continue;
+        bool listed = false;
+        for (auto& cand : b.coproduce) listed = listed || cand.first == u;
+        if (listed) continue;
+        b.sibling = u;
+        int node = buildNode(b, u, umap);
+        b.sibling = 0xffffffffu;
+        if (slot_of[u] < 0 && !produced.count(u)) b.coproduce.push_back({u, node});
+      }
+    }
     // Without any reduction the trailing dims form the column space: enough of them to give a
     // row at least 1024 elements, so flat elementwise programs still fill the machine.
     if (!b.cols_fixed) {

@@ -347,7 +347,8 @@ def test_a_fold_over_rows_and_columns_joins_the_row_kernel_of_its_operand(cpu_se
 def test_row_statistics_needed_elsewhere_leave_the_kernel_that_computes_them_anyway(cpu_session):
     """value_and_grad of the layer-norm loss: the gradient with respect to x needs the row means and
     variances; the gradient of the gain, a fold over the rows, needs them too.  They are written by the first
-    kernel (three outputs) instead of being computed again from x by kernels of their own."""
+    kernel instead of being computed again from x by kernels of their own, and the rows' shares of the
+    value (a fold over the same columns of an operand with the same dims) join that kernel too."""
     def loss(b, a):
         x, gain, target = a
         centred = x.sub(x.mean("c"))
@@ -358,6 +359,8 @@ def test_row_statistics_needed_elsewhere_leave_the_kernel_that_computes_them_any
     compiled = cpu_session.compile(tensor.define("layer_norm_loss", specs, loss).value_and_grad([0, 1]))
     lines = [l.strip() for l in compiled.plan_summary().strip().split("\n") if l.strip().startswith("row kernel")]
     cpu_session.release(compiled)
-    assert len(lines) == 4
-    assert "rows=8192 cols=4096" in lines[0] and "outputs=3" in lines[0]
+    # the rows' shares of the value join the same kernel: x and the target are read by two kernels, not five
+    assert len(lines) == 3
+    assert "rows=8192 cols=4096" in lines[0] and "reduces=5" in lines[0] and "outputs=4" in lines[0]
     assert "rows=4096 cols=8192" in lines[1] and "tpr=1 rpc=256" in lines[1]
+    assert "rows=1 cols=8192" in lines[2]

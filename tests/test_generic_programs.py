@@ -364,3 +364,41 @@ def test_row_statistics_needed_elsewhere_leave_the_kernel_that_computes_them_any
     assert "rows=8192 cols=4096" in lines[0] and "reduces=5" in lines[0] and "outputs=4" in lines[0]
     assert "rows=4096 cols=8192" in lines[1] and "tpr=1 rpc=256" in lines[1]
     assert "rows=1 cols=8192" in lines[2]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(12))
+def test_random_gradient_and_multi_output_programs_match_oracle(gpu_session, seed):
+    """The random programs above once more, as a scalar loss under value_and_grad (three outputs: the value
+    and the gradients with respect to both full-shaped inputs) and as a program with up to four outputs of
+    different shapes (the result, its square, its row sums, its column maxima): every output against the
+    reference-order and the f64 evaluation of the very same derived program."""
+    specs, body, inputs = random_sum_program(400 + seed)
+
+    def loss(b, a):
+        out = body(b, a)
+        return out.sum([name for name, _ in out.ty.dims])
+
+    def several(b, a):
+        out = body(b, a)
+        names = [name for name, _ in out.ty.dims]
+        outs = [out, out.mul(out)]
+        if "c" in names:
+            outs.append(out.sum("c"))
+        if "r" in names:
+            outs.append(out.max("r"))
+        return outs
+
+    programs = [tensor.define("random_loss_%d" % seed, specs, loss).value_and_grad([0, 1]),
+                tensor.define("random_outputs_%d" % seed, specs, several)]
+    for program in programs:
+        compiled = gpu_session.compile(program)
+        outs = [np.empty(d.byte_size, np.uint8) for d in compiled.output_descriptors()]
+        gpu_session.invoke(compiled, inputs, outs)
+        gpu_session.release(compiled)
+        ref = oracle.run(program.wire, inputs, mode="ref")
+        exact = oracle.run(program.wire, inputs, mode="f64")
+        for j, (got, want, ex) in enumerate(zip(outs, ref, exact)):
+            check_three_distances("%s output %d" % (program.name, j),
+                                  got.view(np.float32).astype(np.float64), np.asarray(want, np.float64).reshape(-1),
+                                  np.asarray(ex, np.float64).reshape(-1), 1e-4)
